@@ -1,0 +1,141 @@
+// Shared device helpers for the hkv kernels (sm_100a): error codes, workspace header, mbarrier / bulk-copy / mma /
+// narrow-float conversion wrappers. Everything here is inline PTX or plain CUDA; no library calls.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/hkv.h"
+
+namespace hkv {
+
+// ---------------------------------------------------------------------------------------------------- workspace
+// Layout of the decode workspace (all offsets from the 256-byte aligned base):
+//   Header | PartDesc[n_parts] | lse[n_parts][2][RPAD] fp32 | opart[n_parts][2][RPAD][D] fp32
+// Each decode partition (one CTA) owns two partial slots: slot 0 for a sequence piece that begins the partition,
+// slot 1 for a piece that ends it while the sequence continues in the next partition.
+struct Header {
+  int status;      // HKV_OK or HKV_ERR_DEVICE_WAIT, set by a kernel whose bounded wait ran out
+  int n_parts;     // partitions used by the last decode launch
+  int per;         // stream units (16-token blocks of one kv head) per partition
+  int total;       // stream units in total
+  int pad[12];
+};
+
+struct PartDesc {
+  int b;           // request of the partition's first piece (-1: the partition is empty)
+  int h;           // kv head of that piece
+  int blk_begin;   // first 16-token block of the piece inside its sequence
+  int blk_end;     // one past its last block
+  int units;       // blocks in the whole sequence (per kv head)
+  int first_part;  // partition holding the sequence's first block
+  int first_slot;  // partial slot used by that first partition for this sequence (0 or 1)
+  int pad;
+};
+
+constexpr int kMaxBatch = 8192;          // requests per decode call (coarse prefix table lives in shared memory)
+constexpr long long kWaitCycles = 1ll << 32;   // bound of every device-side wait, in SM clock cycles (about 2 s)
+
+__host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct WorkspaceLayout {
+  size_t desc_off, lse_off, opart_off, total;
+  __host__ __device__ WorkspaceLayout(int n_parts, int rpad, int D) {
+    desc_off = align_up(sizeof(Header), 256);
+    lse_off = align_up(desc_off + sizeof(PartDesc) * (size_t)n_parts, 256);
+    opart_off = align_up(lse_off + sizeof(float) * (size_t)n_parts * 2 * rpad, 256);
+    total = align_up(opart_off + sizeof(float) * (size_t)n_parts * 2 * rpad * D, 256);
+  }
+};
+
+// ------------------------------------------------------------------------------------------------------ mbarrier
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: returns false when the phase did not complete within kWaitCycles (the caller records the failure and
+// leaves its loop; nothing spins for ever).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kWaitCycles) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 1-D bulk copy global -> shared of `bytes` (multiple of 16, both addresses 16-byte aligned), completion counted on
+// the mbarrier. No multicast, this CTA's shared memory only.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------- conversions
+// four E2M1 pairs (the 4 bytes of w) -> four f16x2; low nibble of each byte in the low half
+__device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t w, uint32_t (&o)[4]) {
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3])
+      : "r"(w));
+}
+// two E4M3 bytes (low 16 bits of x) -> f16x2, low byte in the low half. 0x7f / 0xff give NaN.
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t x) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"((unsigned short)x));
+  return r;
+}
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+}  // namespace hkv

@@ -1,0 +1,720 @@
+// Paged split-K flash-decoding over the NVFP4 KV cache, and the log-sum-exp combine (sm_100a).
+//
+// Work decomposition ("balanced split-K"): the unit of work is one 16-token block of one (request, kv head)
+// sequence. All units of a batch, ordered (request, kv head, block), form one stream that is cut into equal
+// partitions, one per CTA of a grid that fills the GPU exactly once. A CTA therefore streams the same number of
+// cache bytes as every other CTA whatever the mix of context lengths. Inside a partition, a run of units of the same
+// (request, kv head) is a *piece*. A piece that covers its whole sequence is finished by the CTA and written to the
+// output; other pieces leave a normalised fp32 partial and a log2-sum-exp in the workspace, which the combine kernel
+// merges in partition order (fixed order => deterministic results).
+//
+// Inside a CTA, TG warps take the partition's units round-robin. Every warp owns a private ring of NS shared-memory
+// stages; it issues 1-D bulk copies (cp.async.bulk, completion on an mbarrier) for its own future units, driven by
+// the block table, and consumes them in order, so the main loop needs no cross-warp synchronisation. Per unit a warp
+// computes S = Q K^T with mma.m16n8k16 (A = query rows padded to 16, B = 16 keys dequantised in registers from E2M1
+// codes with cvt.rn.f16x2.e2m1x2 and one f16x2 multiply by the E4M3 block scale), a warp-shuffle online softmax in the
+// log2 domain, and O^T += V^T P^T with A = dequantised values. code * scale is exact in f16 (at most 5 significant
+// bits, magnitude in [2^-10, 2688]), so the only roundings are P to f16 and the fp32 accumulations.
+// At the end of a piece the TG warps merge their (max, sum, accumulator) states through shared memory.
+//
+// Every wait on an mbarrier is bounded (hkv::kWaitCycles); when one runs out the kernel records
+// HKV_ERR_DEVICE_WAIT in the workspace header, stops consuming and returns.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "hkv_common.cuh"
+
+namespace hkv {
+
+constexpr int TG = 4;            // consumer warps per CTA
+constexpr int NTHREADS = TG * 32;
+constexpr int RPAD = 8;          // query rows per (request, kv head) padded to the mma N tile
+constexpr float NEG_BIG = -1.0e30f;
+constexpr float TAU = 8.0f;      // lazy rescale threshold (log2 domain): P stays below 2^8, inside f16's range
+
+struct DecodeParams {
+  const __nv_bfloat16* q;
+  const uint8_t* kd;
+  const uint8_t* ksf;
+  const uint8_t* vd;
+  const uint8_t* vsf;
+  long long dsp, dst, dsh, ssp, sst, ssh;
+  const int* bt;
+  const int* seq_lens;
+  const int* qsl;
+  const float* gk;
+  const float* gv;
+  uint8_t* ws;
+  __nv_bfloat16* out;
+  int MP, B, KVH, G, qlmax, PS;
+  float scale_log2, v_scale;
+};
+
+// Shared-memory geometry of one stage (K tile then V tile of 16 tokens) for head_dim D and cache layout LAYOUT:
+//   LAYOUT 0  token rows of [D/2 code bytes | D/16 scale bytes] back to back (the serving "slot" layout with heads
+//             outermost inside a page): one bulk copy of 16 * slot bytes per tile
+//   LAYOUT 1  16 code rows back to back, then 16 scale rows (the page-region layout of the reference's torch oracle):
+//             two bulk copies per tile
+template <int D, int LAYOUT>
+struct Geo {
+  static constexpr int SD = D / 2, SS = D / 16, SLOT = SD + SS;
+  static constexpr int TILE = 16 * SLOT;               // bytes of one (head, side) tile of 16 tokens
+  static constexpr int STAGE = 2 * TILE;
+  static constexpr int ROW = LAYOUT == 0 ? SLOT : SD;  // byte stride between code rows in shared memory
+  static constexpr int SF_BASE = LAYOUT == 0 ? SD : 16 * SD;
+  static constexpr int SF_ROW = LAYOUT == 0 ? SLOT : SS;
+  static constexpr int KS = D / 16;                    // k-steps of Q K^T == mma tiles of P V
+  static constexpr int NBL = D / 64;                   // 16-channel blocks of one key row held by one lane
+  static constexpr int NH = D / 128;                   // 16-channel blocks of one value row held by one lane
+  // token handled by column n of score tile t (chosen so that the value loads of a warp hit distinct banks)
+  __device__ static constexpr int tok(int t, int n) { return (D == 128 && LAYOUT == 0) ? 2 * n + t : n + 8 * t; }
+  // 16-channel block of a key row held by lane column c as its u-th block
+  __device__ static constexpr int kblk(int c, int u) { return D == 128 ? c + 4 * u : 2 * c + (u & 1) + 8 * (u >> 1); }
+};
+
+// walks the (request, kv head) sequences of the unit stream; all fields are warp-uniform
+struct ReqInfo {
+  int U, L, ql, q0;
+};
+__device__ __forceinline__ ReqInfo load_req(const DecodeParams& p, int b) {
+  ReqInfo r;
+  r.q0 = __ldg(p.qsl + b);
+  int ql = __ldg(p.qsl + b + 1) - r.q0;
+  ql = (ql < 0 || ql > p.qlmax) ? 0 : ql;
+  r.ql = ql;
+  r.L = ql > 0 ? max(__ldg(p.seq_lens + b), 0) : 0;
+  r.U = ql > 0 ? max(1, (r.L + 15) >> 4) : 0;
+  return r;
+}
+
+template <int D, int LAYOUT, int NS>
+struct Smem {
+  using G_ = Geo<D, LAYOUT>;
+  static constexpr int RING = TG * NS * G_::STAGE;
+  static constexpr int BARS = TG * NS * 8;
+  static constexpr int OROW = D + 4;                               // padded accumulator row (floats)
+  static constexpr int MERGE = TG * RPAD * OROW * 4 + TG * RPAD * 2 * 4;
+  static constexpr int COARSE = (kMaxBatch / 32 + 2) * 4;
+  static constexpr int TOTAL = RING + BARS + MERGE + COARSE + 64;
+};
+
+template <int D, int LAYOUT, int NS>
+__global__ void __launch_bounds__(NTHREADS) decode_kernel(const DecodeParams p) {
+  using Gm = Geo<D, LAYOUT>;
+  using Sm = Smem<D, LAYOUT, NS>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* ring = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Sm::RING);
+  float* obuf = reinterpret_cast<float*>(smem + Sm::RING + Sm::BARS);
+  float* mbuf = obuf + TG * RPAD * Sm::OROW;
+  float* lbuf = mbuf + TG * RPAD;
+  int* coarse = reinterpret_cast<int*>(smem + Sm::RING + Sm::BARS + Sm::MERGE);
+
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, c = lane & 3;
+  const int KVH = p.KVH, B = p.B;
+  Header* hdr = reinterpret_cast<Header*>(p.ws);
+  const int n_parts = gridDim.x, part = blockIdx.x;
+  const WorkspaceLayout wl(n_parts, RPAD, D);
+  PartDesc* descs = reinterpret_cast<PartDesc*>(p.ws + wl.desc_off);
+  float* lse_ws = reinterpret_cast<float*>(p.ws + wl.lse_off);
+  float* opart_ws = reinterpret_cast<float*>(p.ws + wl.opart_off);
+
+  // ---- coarse prefix of units per request: coarse[k] = sum of U_b over b < 32 k
+  const int ngrp = (B + 31) >> 5;
+  for (int grp = w; grp < ngrp; grp += TG) {
+    const int b = grp * 32 + lane;
+    int u = b < B ? load_req(p, b).U : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) u += __shfl_xor_sync(0xffffffffu, u, o);
+    if (lane == 0) coarse[grp + 1] = u;
+  }
+  if (tid < TG * NS) mbar_init(bars + tid, 1);
+  __syncthreads();
+  if (w == 0) {                                   // exclusive scan of up to kMaxBatch / 32 group sums
+    const int per_lane = (ngrp + 31) >> 5;
+    int s = 0;
+    for (int i = 0; i < per_lane; ++i) {
+      const int k = lane * per_lane + i;
+      s += k < ngrp ? coarse[k + 1] : 0;
+    }
+    int incl = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    int run = incl - s;
+    for (int i = 0; i < per_lane; ++i) {
+      const int k = lane * per_lane + i;
+      if (k < ngrp) {
+        const int v = coarse[k + 1];
+        coarse[k + 1] = run + v;                  // inclusive: coarse[k + 1] = units of requests < 32 (k + 1)
+        run += v;
+      }
+    }
+    if (lane == 0) coarse[0] = 0;
+  }
+  fence_barrier_init();
+  __syncthreads();
+
+  const long long total = (long long)coarse[ngrp] * KVH;
+  const int per = (int)max(1ll, (total + n_parts - 1) / n_parts);
+  const long long lo = (long long)part * per;
+  const long long hi = min(total, lo + per);
+  if (part == 0 && tid == 0) {
+    hdr->n_parts = n_parts;
+    hdr->per = per;
+    hdr->total = (int)total;
+  }
+  if (lo >= hi) {
+    if (tid == 0) descs[part].b = -1;
+    return;
+  }
+  const int n_units = (int)(hi - lo);
+
+  // ---- locate the request that holds stream position lo (warp-uniform, every warp for itself)
+  int b0, base0;                                   // request and units of earlier requests (per head)
+  {
+    int lo_g = 0, hi_g = ngrp;                     // largest grp with coarse[grp] * KVH <= lo
+    while (hi_g - lo_g > 1) {
+      const int mid = (lo_g + hi_g) >> 1;
+      if ((long long)coarse[mid] * KVH <= lo) lo_g = mid; else hi_g = mid;
+    }
+    const int b = lo_g * 32 + lane;
+    const int u = b < B ? load_req(p, b).U : 0;
+    int incl = u;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    const unsigned hit = __ballot_sync(0xffffffffu, (long long)(coarse[lo_g] + incl) * KVH > lo);
+    const int j = __ffs(hit) - 1;                  // first request whose end lies beyond lo
+    b0 = lo_g * 32 + j;
+    base0 = coarse[lo_g] + __shfl_sync(0xffffffffu, incl - u, j);
+  }
+
+  // ---- fetch side: walks this warp's units (local index k = w, w + TG, ..) and issues their bulk copies
+  struct Walker {
+    int b, h, blk;
+    long long seq0;                                // stream position of block 0 of (b, h)
+    ReqInfo r;
+  };
+  auto seek = [&](Walker& wk, long long pos) {     // move to the sequence that holds pos (pos < total)
+    while (true) {
+      const long long end_h = wk.seq0 + wk.r.U;
+      if (pos < end_h) break;
+      wk.seq0 = end_h;
+      if (++wk.h == KVH) {
+        wk.h = 0;
+        do { wk.r = load_req(p, ++wk.b); } while (wk.r.U == 0);
+      }
+    }
+    wk.blk = (int)(pos - wk.seq0);
+  };
+  Walker fw, cw;
+  fw.b = b0;
+  fw.r = load_req(p, b0);
+  fw.h = (int)((lo - (long long)base0 * KVH) / fw.r.U);
+  fw.seq0 = (long long)base0 * KVH + (long long)fw.h * fw.r.U;
+  fw.blk = 0;
+  cw = fw;
+
+  const int n_my = n_units > w ? (n_units - w + TG - 1) / TG : 0;
+  uint8_t* my_ring = ring + w * NS * Gm::STAGE;
+  uint64_t* my_bars = bars + w * NS;
+  int pg_b = -1, pg_h = -1, pg_blk0 = 0;            // block-table prefetch window of the fetch walker
+  int pg = 0;
+
+  auto issue_fetch = [&](int fi) {
+    const long long pos = lo + w + (long long)fi * TG;
+    seek(fw, pos);
+    const int nvalid = min(16, fw.r.L - 16 * fw.blk);
+    if (nvalid <= 0) return;                        // empty context: nothing to read
+    // page ids of this warp's next 32 units of the same sequence, one per lane
+    const int rel = (fw.blk - pg_blk0) / TG;
+    if (pg_b != fw.b || pg_h != fw.h || (fw.blk - pg_blk0) % TG != 0 || rel < 0 || rel >= 32) {
+      pg_b = fw.b; pg_h = fw.h; pg_blk0 = fw.blk;
+      const int blk_l = fw.blk + lane * TG;
+      pg = blk_l < fw.r.U ? __ldg(p.bt + (long long)fw.b * p.MP + (blk_l * 16) / p.PS) : 0;
+    }
+    const int page = __shfl_sync(0xffffffffu, pg, (fw.blk - pg_blk0) / TG);
+    const int pos0 = (fw.blk * 16) % p.PS;
+    const int slot = fi % NS;
+    uint8_t* st = my_ring + slot * Gm::STAGE;
+    uint64_t* bar = my_bars + slot;
+    if (lane == 0) mbar_expect_tx(bar, Gm::STAGE);
+    __syncwarp();
+    const long long doff = (long long)page * p.dsp + (long long)pos0 * p.dst + (long long)fw.h * p.dsh;
+    if (LAYOUT == 0) {
+      if (lane == 0) bulk_g2s(st, p.kd + doff, Gm::TILE, bar);
+      if (lane == 1) bulk_g2s(st + Gm::TILE, p.vd + doff, Gm::TILE, bar);
+    } else {
+      const long long soff = (long long)page * p.ssp + (long long)pos0 * p.sst + (long long)fw.h * p.ssh;
+      if (lane == 0) bulk_g2s(st, p.kd + doff, 16 * Gm::SD, bar);
+      if (lane == 1) bulk_g2s(st + 16 * Gm::SD, p.ksf + soff, 16 * Gm::SS, bar);
+      if (lane == 2) bulk_g2s(st + Gm::TILE, p.vd + doff, 16 * Gm::SD, bar);
+      if (lane == 3) bulk_g2s(st + Gm::TILE + 16 * Gm::SD, p.vsf + soff, 16 * Gm::SS, bar);
+    }
+  };
+
+  int fi = 0, ci = 0;
+  uint32_t phase_bits = 0;                          // bit s: parity the next wait on stage s must see
+  bool dead = false;                                // a bounded wait ran out: stop consuming
+  for (; fi < min(NS, n_my); ++fi) issue_fetch(fi);
+
+  // ---- compute side: walk the pieces of the partition
+  long long pos = lo;
+  int piece_idx = 0;
+  while (pos < hi) {
+    seek(cw, pos);
+    const int blk0 = cw.blk;
+    const long long seq_end = cw.seq0 + cw.r.U;
+    const long long piece_end = min(hi, seq_end);
+    const int n_piece = (int)(piece_end - pos);
+    const int k0 = (int)(pos - lo);                 // partition-local index of the piece's first unit
+    const int b = cw.b, h = cw.h, L = cw.r.L, ql = cw.r.ql, q0 = cw.r.q0, G = p.G;
+    const int R = G * ql;
+    const bool complete = blk0 == 0 && piece_end == seq_end;
+    if (piece_idx == 0 && tid == 0) {
+      PartDesc d;
+      d.b = b; d.h = h; d.blk_begin = blk0; d.blk_end = blk0 + n_piece; d.units = cw.r.U;
+      d.first_part = (int)(cw.seq0 / per);
+      d.first_slot = cw.seq0 == (long long)d.first_part * per ? 0 : 1;
+      d.pad = 0;
+      descs[part] = d;
+    }
+
+    // this warp's units of the piece: local indices k = k_first, k_first + TG, .. < k0 + n_piece
+    const int k_first = k0 + ((w - k0) % TG + TG) % TG;
+    float m_run = NEG_BIG, l_run = 0.0f;
+    float o[Gm::KS][4];
+#pragma unroll
+    for (int j = 0; j < Gm::KS; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+
+    if (k_first < k0 + n_piece && !dead) {
+      // query fragments: row g of the (request, kv head) group, channels of this lane's key blocks, as f16
+      uint32_t qa[Gm::KS][2];
+      {
+        const bool have = g < R;
+        const int t = have ? g / G : 0, gq = have ? g - t * G : 0;
+        const __nv_bfloat16* qrow = p.q + ((long long)(q0 + t) * (KVH * G) + h * G + gq) * D;
+#pragma unroll
+        for (int u = 0; u < Gm::NBL; ++u) {
+          uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
+          if (have) {
+            const uint4* src = reinterpret_cast<const uint4*>(qrow + 16 * Gm::kblk(c, u));
+            x0 = __ldg(src);
+            x1 = __ldg(src + 1);
+          }
+          const uint32_t ws[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float a = __uint_as_float(ws[i] << 16), bq = __uint_as_float(ws[i] & 0xffff0000u);
+            a = fminf(fmaxf(a, -65504.0f), 65504.0f);
+            bq = fminf(fmaxf(bq, -65504.0f), 65504.0f);
+            qa[4 * u + (i >> 1)][i & 1] = pack_f16x2(a, bq);
+          }
+        }
+      }
+      const float sc = p.scale_log2 * __ldg(p.gk + h);
+      // visible context of this lane's query row (causal among the request's own query tokens)
+      const int lim = g < R ? L - ql + g / G + 1 : L;
+      const int lim_min = L - ql + 1;
+
+      for (int k = k_first; k < k0 + n_piece; k += TG) {
+        const int blk = blk0 + (k - k0);
+        const int tbase = blk * 16;
+        const int nvalid = min(16, L - tbase);
+        if (nvalid > 0) {
+          const int slot = ci % NS;
+          if (!mbar_wait_bounded(my_bars + slot, (phase_bits >> slot) & 1u)) {
+            if (lane == 0) atomicExch(&hdr->status, HKV_ERR_DEVICE_WAIT);
+            dead = true;
+            break;
+          }
+          phase_bits ^= 1u << slot;
+          const uint8_t* kt = my_ring + slot * Gm::STAGE;
+          const uint8_t* vt = kt + Gm::TILE;
+
+          // ---------------- S = Q K^T : two score tiles of 8 tokens each, rows = query rows
+          float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+          const int r0 = Gm::tok(0, g), r1 = Gm::tok(1, g);
+#pragma unroll
+          for (int u = 0; u < Gm::NBL; ++u) {
+            const int kb = Gm::kblk(c, u);
+            const uint2 w0 = *reinterpret_cast<const uint2*>(kt + r0 * Gm::ROW + 8 * kb);
+            const uint2 w1 = *reinterpret_cast<const uint2*>(kt + r1 * Gm::ROW + 8 * kb);
+            const uint32_t f0 = kt[Gm::SF_BASE + r0 * Gm::SF_ROW + kb], f1 = kt[Gm::SF_BASE + r1 * Gm::SF_ROW + kb];
+            const uint32_t sf0 = e4m3x2_to_f16x2(f0 | (f0 << 8)), sf1 = e4m3x2_to_f16x2(f1 | (f1 << 8));
+            uint32_t e0[4], e1[4], e2[4], e3[4];
+            e2m1x8_to_f16x2(w0.x, e0);
+            e2m1x8_to_f16x2(w0.y, e1);
+            e2m1x8_to_f16x2(w1.x, e2);
+            e2m1x8_to_f16x2(w1.y, e3);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              e0[i] = hmul2(e0[i], sf0);
+              e1[i] = hmul2(e1[i], sf0);
+              e2[i] = hmul2(e2[i], sf1);
+              e3[i] = hmul2(e3[i], sf1);
+            }
+            mma_f16(s0, qa[4 * u + 0][0], 0u, qa[4 * u + 0][1], 0u, e0[0], e0[1]);
+            mma_f16(s0, qa[4 * u + 1][0], 0u, qa[4 * u + 1][1], 0u, e0[2], e0[3]);
+            mma_f16(s0, qa[4 * u + 2][0], 0u, qa[4 * u + 2][1], 0u, e1[0], e1[1]);
+            mma_f16(s0, qa[4 * u + 3][0], 0u, qa[4 * u + 3][1], 0u, e1[2], e1[3]);
+            mma_f16(s1, qa[4 * u + 0][0], 0u, qa[4 * u + 0][1], 0u, e2[0], e2[1]);
+            mma_f16(s1, qa[4 * u + 1][0], 0u, qa[4 * u + 1][1], 0u, e2[2], e2[3]);
+            mma_f16(s1, qa[4 * u + 2][0], 0u, qa[4 * u + 2][1], 0u, e3[0], e3[1]);
+            mma_f16(s1, qa[4 * u + 3][0], 0u, qa[4 * u + 3][1], 0u, e3[2], e3[3]);
+          }
+
+          // ---------------- online softmax for query row g over this lane's 4 tokens
+          const int t00 = Gm::tok(0, 2 * c), t01 = Gm::tok(0, 2 * c + 1), t10 = Gm::tok(1, 2 * c),
+                    t11 = Gm::tok(1, 2 * c + 1);
+          float x0 = s0[0] * sc, x1 = s0[1] * sc, x2 = s1[0] * sc, x3 = s1[1] * sc;
+          if (tbase + 16 > lim_min) {                 // warp-uniform: only the last block(s) of a sequence
+            const float ninf = -__int_as_float(0x7f800000);
+            x0 = tbase + t00 < lim ? x0 : ninf;
+            x1 = tbase + t01 < lim ? x1 : ninf;
+            x2 = tbase + t10 < lim ? x2 : ninf;
+            x3 = tbase + t11 < lim ? x3 : ninf;
+          }
+          float bm = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
+          bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+          bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+          bm = fmaxf(bm, NEG_BIG);
+          if (__any_sync(0xffffffffu, bm > m_run + TAU)) {
+            const float m_new = fmaxf(m_run, bm);
+            const float alpha = fast_exp2(m_run - m_new);
+            m_run = m_new;
+            l_run *= alpha;
+            const float a0 = __shfl_sync(0xffffffffu, alpha, 8 * c), a1 = __shfl_sync(0xffffffffu, alpha, 8 * c + 4);
+#pragma unroll
+            for (int j = 0; j < Gm::KS; ++j) {
+              o[j][0] *= a0; o[j][1] *= a1; o[j][2] *= a0; o[j][3] *= a1;
+            }
+          }
+          const float p0 = fast_exp2(x0 - m_run), p1 = fast_exp2(x1 - m_run), p2 = fast_exp2(x2 - m_run),
+                      p3 = fast_exp2(x3 - m_run);
+          l_run += (p0 + p1) + (p2 + p3);
+          const uint32_t pb0 = pack_f16x2(p0, p1), pb1 = pack_f16x2(p2, p3);
+
+          // ---------------- O^T += V^T P^T : rows = channels of block g (+8), columns = query rows
+          const bool tail = nvalid < 16;
+#pragma unroll
+          for (int hf = 0; hf < Gm::NH; ++hf) {
+            const int vb = g + 8 * hf;
+            const uint2 v00 = *reinterpret_cast<const uint2*>(vt + t00 * Gm::ROW + 8 * vb);
+            const uint2 v01 = *reinterpret_cast<const uint2*>(vt + t01 * Gm::ROW + 8 * vb);
+            const uint2 v10 = *reinterpret_cast<const uint2*>(vt + t10 * Gm::ROW + 8 * vb);
+            const uint2 v11 = *reinterpret_cast<const uint2*>(vt + t11 * Gm::ROW + 8 * vb);
+            uint32_t f00 = vt[Gm::SF_BASE + t00 * Gm::SF_ROW + vb], f01 = vt[Gm::SF_BASE + t01 * Gm::SF_ROW + vb];
+            uint32_t f10 = vt[Gm::SF_BASE + t10 * Gm::SF_ROW + vb], f11 = vt[Gm::SF_BASE + t11 * Gm::SF_ROW + vb];
+            if (tail) {                               // rows past the context hold arbitrary bytes: read them as 0
+              f00 = t00 < nvalid ? f00 : 0u;
+              f01 = t01 < nvalid ? f01 : 0u;
+              f10 = t10 < nvalid ? f10 : 0u;
+              f11 = t11 < nvalid ? f11 : 0u;
+            }
+            const uint32_t sa = e4m3x2_to_f16x2(f00 | (f01 << 8)), sb = e4m3x2_to_f16x2(f10 | (f11 << 8));
+            // bytes of (token pair, channel): low nibble = first token of the pair, high nibble = second
+            const uint32_t M = 0x0f0f0f0fu;
+            const uint32_t xe0 = (v00.x & M) | ((v01.x & M) << 4), xo0 = ((v00.x >> 4) & M) | (v01.x & ~M);
+            const uint32_t xe1 = (v00.y & M) | ((v01.y & M) << 4), xo1 = ((v00.y >> 4) & M) | (v01.y & ~M);
+            const uint32_t ye0 = (v10.x & M) | ((v11.x & M) << 4), yo0 = ((v10.x >> 4) & M) | (v11.x & ~M);
+            const uint32_t ye1 = (v10.y & M) | ((v11.y & M) << 4), yo1 = ((v10.y >> 4) & M) | (v11.y & ~M);
+            uint32_t ae[8], ao[8], be[8], bo[8];      // [channel pair jj] -> f16x2 over (first, second) token
+            {
+              uint32_t t4[4];
+              e2m1x8_to_f16x2(xe0, t4); ae[0] = t4[0]; ae[1] = t4[1]; ae[2] = t4[2]; ae[3] = t4[3];
+              e2m1x8_to_f16x2(xe1, t4); ae[4] = t4[0]; ae[5] = t4[1]; ae[6] = t4[2]; ae[7] = t4[3];
+              e2m1x8_to_f16x2(xo0, t4); ao[0] = t4[0]; ao[1] = t4[1]; ao[2] = t4[2]; ao[3] = t4[3];
+              e2m1x8_to_f16x2(xo1, t4); ao[4] = t4[0]; ao[5] = t4[1]; ao[6] = t4[2]; ao[7] = t4[3];
+              e2m1x8_to_f16x2(ye0, t4); be[0] = t4[0]; be[1] = t4[1]; be[2] = t4[2]; be[3] = t4[3];
+              e2m1x8_to_f16x2(ye1, t4); be[4] = t4[0]; be[5] = t4[1]; be[6] = t4[2]; be[7] = t4[3];
+              e2m1x8_to_f16x2(yo0, t4); bo[0] = t4[0]; bo[1] = t4[1]; bo[2] = t4[2]; bo[3] = t4[3];
+              e2m1x8_to_f16x2(yo1, t4); bo[4] = t4[0]; bo[5] = t4[1]; bo[6] = t4[2]; bo[7] = t4[3];
+            }
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj)
+              mma_f16(o[8 * hf + jj], hmul2(ae[jj], sa), hmul2(ao[jj], sa), hmul2(be[jj], sb), hmul2(bo[jj], sb), pb0,
+                      pb1);
+          }
+          __syncwarp();
+        }
+        ++ci;
+        if (fi < n_my) {
+          issue_fetch(fi);
+          ++fi;
+        }
+      }
+    }
+
+    // ---------------- merge the TG warps' states of this piece and write it out
+    {
+      float l_tot = l_run;
+      l_tot += __shfl_xor_sync(0xffffffffu, l_tot, 1);
+      l_tot += __shfl_xor_sync(0xffffffffu, l_tot, 2);
+      if (c == 0) {
+        mbuf[w * RPAD + g] = m_run;
+        lbuf[w * RPAD + g] = l_tot;
+      }
+      float* ob = obuf + (size_t)w * RPAD * Sm::OROW;
+#pragma unroll
+      for (int hf = 0; hf < Gm::NH; ++hf)
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const int ch = 16 * (g + 8 * hf) + 2 * jj;
+          const float* a = o[8 * hf + jj];
+          *reinterpret_cast<float2*>(ob + (2 * c) * Sm::OROW + ch) = make_float2(a[0], a[2]);
+          *reinterpret_cast<float2*>(ob + (2 * c + 1) * Sm::OROW + ch) = make_float2(a[1], a[3]);
+        }
+      __syncthreads();
+      const float gvh = __ldg(p.gv + h);
+      const int slot_id = part * 2 + (piece_idx == 0 ? 0 : 1);
+      for (int idx = tid; idx < R * (D / 2); idx += NTHREADS) {
+        const int row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
+        float mx = NEG_BIG;
+#pragma unroll
+        for (int ww = 0; ww < TG; ++ww) mx = fmaxf(mx, mbuf[ww * RPAD + row]);
+        float den = 0.0f, n0 = 0.0f, n1 = 0.0f;
+#pragma unroll
+        for (int ww = 0; ww < TG; ++ww) {
+          const float wgt = fast_exp2(mbuf[ww * RPAD + row] - mx);
+          den += lbuf[ww * RPAD + row] * wgt;
+          const float2 v = *reinterpret_cast<const float2*>(obuf + ((size_t)ww * RPAD + row) * Sm::OROW + ch);
+          n0 += v.x * wgt;
+          n1 += v.y * wgt;
+        }
+        const float inv = den > 0.0f ? gvh / den : 0.0f;
+        if (complete) {
+          const int t = row / G, gq = row - t * G;
+          __nv_bfloat16* dst = p.out + ((long long)(q0 + t) * (KVH * G) + h * G + gq) * D + ch;
+          *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(n0 * inv * p.v_scale, n1 * inv * p.v_scale);
+        } else {
+          *reinterpret_cast<float2*>(opart_ws + ((size_t)slot_id * RPAD + row) * D + ch) = make_float2(n0 * inv, n1 * inv);
+          if (ch == 0) lse_ws[slot_id * RPAD + row] = den > 0.0f ? log2f(den) + mx : -__int_as_float(0x7f800000);
+        }
+      }
+      __syncthreads();
+    }
+    pos = piece_end;
+    ++piece_idx;
+  }
+
+  // a warp that gave up may still have copies in flight: wait for them (bounded) before the CTA's shared memory is
+  // released
+  if (dead) {
+    for (int i = 0; i < NS; ++i) (void)mbar_wait_bounded(my_bars + i, (phase_bits >> i) & 1u);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------- combine
+// One CTA per decode partition. A partition whose FIRST piece ends a sequence that began in an earlier partition
+// merges that sequence: pieces live in slot `first_slot` of partition `first_part`, slot 0 of every partition in
+// between, and slot 0 of this one. Weights w_i = 2^(lse_i - max) / sum, summed in partition order.
+template <int D>
+__global__ void __launch_bounds__(128) combine_kernel(const uint8_t* ws, const int* qsl, __nv_bfloat16* out, int KVH,
+                                                      int G, int qlmax, float v_scale) {
+  const int part = blockIdx.x, tid = threadIdx.x;
+  const int n_parts = reinterpret_cast<const Header*>(ws)->n_parts;   // written by the preceding decode launch
+  if (part >= n_parts) return;
+  const WorkspaceLayout wl(n_parts, RPAD, D);
+  const PartDesc d = reinterpret_cast<const PartDesc*>(ws + wl.desc_off)[part];
+  if (d.b < 0 || d.blk_begin == 0 || d.blk_end != d.units) return;
+  const float* lse_ws = reinterpret_cast<const float*>(ws + wl.lse_off);
+  const float* opart_ws = reinterpret_cast<const float*>(ws + wl.opart_off);
+  const int q0 = qsl[d.b];
+  int ql = qsl[d.b + 1] - q0;
+  ql = (ql < 0 || ql > qlmax) ? 0 : ql;
+  const int R = G * ql;
+  const float ninf = -__int_as_float(0x7f800000);
+  for (int idx = tid; idx < R * (D / 2); idx += 128) {
+    const int row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
+    float mx = ninf;
+    for (int pc = d.first_part; pc <= part; ++pc) {
+      const int slot = pc * 2 + (pc == d.first_part ? d.first_slot : 0);
+      mx = fmaxf(mx, lse_ws[slot * RPAD + row]);
+    }
+    float tot = 0.0f, n0 = 0.0f, n1 = 0.0f;
+    for (int pc = d.first_part; pc <= part; ++pc) {
+      const int slot = pc * 2 + (pc == d.first_part ? d.first_slot : 0);
+      const float ls = lse_ws[slot * RPAD + row];
+      if (ls == ninf) continue;                      // an empty piece: its partial is never read
+      const float wgt = exp2f(ls - mx);
+      const float2 v = *reinterpret_cast<const float2*>(opart_ws + ((size_t)slot * RPAD + row) * D + ch);
+      tot += wgt;
+      n0 += v.x * wgt;
+      n1 += v.y * wgt;
+    }
+    const float inv = tot > 0.0f ? v_scale / tot : 0.0f;
+    const int t = row / G, gq = row - t * G;
+    __nv_bfloat16* dst = out + ((long long)(q0 + t) * (KVH * G) + d.h * G + gq) * D + ch;
+    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(n0 * inv, n1 * inv);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------------- host side
+int record_cuda(cudaError_t e);
+
+struct DeviceInfo {
+  int sms = 0;
+  int ctas_per_sm[2][2] = {{0, 0}, {0, 0}};          // [D == 256][LAYOUT]
+  bool ready = false;
+};
+static DeviceInfo g_dev[64];
+
+template <int D, int LAYOUT>
+struct Pick {
+  static constexpr int NS = D == 128 ? 4 : 3;
+};
+
+template <int D, int LAYOUT>
+static cudaError_t setup_variant(int& ctas) {
+  constexpr int NS = Pick<D, LAYOUT>::NS;
+  auto k = decode_kernel<D, LAYOUT, NS>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D, LAYOUT, NS>::TOTAL);
+  if (e != cudaSuccess) return e;
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, k, NTHREADS, Smem<D, LAYOUT, NS>::TOTAL);
+}
+
+static int device_info(DeviceInfo** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return record_cuda(e);
+  if (dev < 0 || dev >= 64) return HKV_ERR_RANGE;
+  DeviceInfo& di = g_dev[dev];
+  if (!di.ready) {
+    e = cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return record_cuda(e);
+    if ((e = setup_variant<128, 0>(di.ctas_per_sm[0][0])) != cudaSuccess) return record_cuda(e);
+    if ((e = setup_variant<128, 1>(di.ctas_per_sm[0][1])) != cudaSuccess) return record_cuda(e);
+    if ((e = setup_variant<256, 0>(di.ctas_per_sm[1][0])) != cudaSuccess) return record_cuda(e);
+    if ((e = setup_variant<256, 1>(di.ctas_per_sm[1][1])) != cudaSuccess) return record_cuda(e);
+    di.ready = true;
+  }
+  *out = &di;
+  return HKV_OK;
+}
+
+// upper bound of partitions for any layout of this head_dim on this device
+static int max_parts(const DeviceInfo& di, int D) {
+  const int i = D == 256;
+  return di.sms * max(1, max(di.ctas_per_sm[i][0], di.ctas_per_sm[i][1]));
+}
+
+}  // namespace hkv
+
+extern "C" size_t hkv_decode_workspace_bytes(int B, int KVH, int G, int D, int qlmax) {
+  using namespace hkv;
+  if (B < 1 || B > kMaxBatch || KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > RPAD || (D != 128 && D != 256)) return 0;
+  DeviceInfo* di;
+  if (device_info(&di) != HKV_OK) return 0;
+  return WorkspaceLayout(max_parts(*di, D), RPAD, D).total;
+}
+
+extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
+                          const int64_t strides[6], int PS, const int32_t* block_tables, int MP,
+                          const int32_t* seq_lens, const int32_t* query_start_loc, int B, int KVH, int G, int D,
+                          int qlmax, float sm_scale, float v_scale, const float* gk, const float* gv, void* workspace,
+                          size_t workspace_bytes, int splits, void* out, void* stream) {
+  using namespace hkv;
+  if (B < 0 || MP < 0) return HKV_ERR_RANGE;
+  if (B == 0) return HKV_OK;
+  if (!q || !kd || !ksf || !vd || !vsf || !strides || !block_tables || !seq_lens || !query_start_loc || !gk || !gv ||
+      !workspace || !out)
+    return HKV_ERR_NULL;
+  if (D != 128 && D != 256) return HKV_ERR_UNSUPPORTED;
+  if (KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > RPAD) return HKV_ERR_UNSUPPORTED;
+  if (PS < 16 || PS % 16 != 0) return HKV_ERR_UNSUPPORTED;
+  if (B > kMaxBatch) return HKV_ERR_RANGE;
+  if (splits < 0) return HKV_ERR_RANGE;
+  if (splits > 64) return HKV_ERR_SPLITS;
+  const int SD = D / 2, SS = D / 16, SLOT = SD + SS;
+  const int64_t dsp = strides[0], dst = strides[1], dsh = strides[2], ssp = strides[3], sst = strides[4],
+                ssh = strides[5];
+  int layout;
+  if (dst == SLOT && sst == SLOT && dsp == ssp && dsh == ssh && (const uint8_t*)ksf == (const uint8_t*)kd + SD &&
+      (const uint8_t*)vsf == (const uint8_t*)vd + SD)
+    layout = 0;
+  else if (dst == SD && sst == SS)
+    layout = 1;
+  else
+    return HKV_ERR_UNSUPPORTED;                      // token rows of a head are not contiguous (positions-outer pages)
+  if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kd | (uintptr_t)vd) & 15) return HKV_ERR_ALIGN;
+  if ((dsp | dsh) & 15) return HKV_ERR_ALIGN;
+  if (layout == 1 && ((((uintptr_t)ksf | (uintptr_t)vsf) & 15) || ((ssp | ssh) & 15))) return HKV_ERR_ALIGN;
+  if ((uintptr_t)workspace & 255) return HKV_ERR_ALIGN;
+  DeviceInfo* di;
+  int rc = device_info(&di);
+  if (rc != HKV_OK) return rc;
+  const int cps = di->ctas_per_sm[D == 256][layout];
+  if (cps < 1) return HKV_ERR_UNSUPPORTED;
+  (void)max_parts;
+  long long n_parts = (long long)di->sms * cps;
+  if (splits > 0) n_parts = std::min<long long>(n_parts, (long long)B * KVH * splits);
+  if (n_parts < 1) n_parts = 1;
+  if (workspace_bytes < WorkspaceLayout((int)n_parts, RPAD, D).total) return HKV_ERR_WORKSPACE;
+  DecodeParams p;
+  p.q = (const __nv_bfloat16*)q;
+  p.kd = (const uint8_t*)kd; p.ksf = (const uint8_t*)ksf; p.vd = (const uint8_t*)vd; p.vsf = (const uint8_t*)vsf;
+  p.dsp = dsp; p.dst = dst; p.dsh = dsh; p.ssp = ssp; p.sst = sst; p.ssh = ssh;
+  p.bt = block_tables; p.seq_lens = seq_lens; p.qsl = query_start_loc;
+  p.gk = gk; p.gv = gv;
+  p.ws = (uint8_t*)workspace;
+  p.out = (__nv_bfloat16*)out;
+  p.MP = MP; p.B = B; p.KVH = KVH; p.G = G; p.qlmax = qlmax; p.PS = PS;
+  p.scale_log2 = sm_scale * 1.4426950408889634f;
+  p.v_scale = v_scale;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned grid = (unsigned)n_parts;
+#define HKV_LAUNCH(DD, LL)                                                                                  \
+  decode_kernel<DD, LL, Pick<DD, LL>::NS><<<grid, NTHREADS, Smem<DD, LL, Pick<DD, LL>::NS>::TOTAL, st>>>(p)
+  if (D == 128) {
+    if (layout == 0) HKV_LAUNCH(128, 0); else HKV_LAUNCH(128, 1);
+  } else {
+    if (layout == 0) HKV_LAUNCH(256, 0); else HKV_LAUNCH(256, 1);
+  }
+#undef HKV_LAUNCH
+  return record_cuda(cudaGetLastError());
+}
+
+extern "C" int hkv_combine(const void* workspace, size_t workspace_bytes, const int32_t* query_start_loc, int B,
+                           int KVH, int G, int D, int qlmax, float v_scale, void* out, void* stream) {
+  using namespace hkv;
+  if (B < 0) return HKV_ERR_RANGE;
+  if (B == 0) return HKV_OK;
+  if (!workspace || !query_start_loc || !out) return HKV_ERR_NULL;
+  if (D != 128 && D != 256) return HKV_ERR_UNSUPPORTED;
+  if (KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > RPAD) return HKV_ERR_UNSUPPORTED;
+  if (((uintptr_t)workspace & 255) || ((uintptr_t)out & 15)) return HKV_ERR_ALIGN;
+  if (workspace_bytes < sizeof(Header)) return HKV_ERR_WORKSPACE;
+  DeviceInfo* di;
+  int rc = device_info(&di);
+  if (rc != HKV_OK) return rc;
+  // the grid covers the largest partition count a decode launch can use on this device; the kernel reads the actual
+  // count from the workspace header
+  const unsigned grid = (unsigned)max_parts(*di, D);
+  if (workspace_bytes < WorkspaceLayout(1, RPAD, D).total) return HKV_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (D == 128)
+    combine_kernel<128><<<grid, 128, 0, st>>>((const uint8_t*)workspace, query_start_loc, (__nv_bfloat16*)out, KVH, G,
+                                              qlmax, v_scale);
+  else
+    combine_kernel<256><<<grid, 128, 0, st>>>((const uint8_t*)workspace, query_start_loc, (__nv_bfloat16*)out, KVH, G,
+                                              qlmax, v_scale);
+  return record_cuda(cudaGetLastError());
+}
+
+extern "C" int hkv_workspace_status(void* workspace, int* status, void* stream) {
+  using namespace hkv;
+  if (!workspace || !status) return HKV_ERR_NULL;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemcpyAsync(status, workspace, sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (e != cudaSuccess) return record_cuda(e);
+  if ((e = cudaMemsetAsync(workspace, 0, sizeof(int), st)) != cudaSuccess) return record_cuda(e);
+  return record_cuda(cudaStreamSynchronize(st));
+}

@@ -1,0 +1,195 @@
+// Quantize-on-write for the NVFP4 paged KV cache (sm_100a).
+//
+// One thread owns one block of 16 consecutive channels of one (token, kv head, side): it reads 32 bytes of bf16,
+// picks the E4M3 block scale (optionally by the 4-candidate squared-error search), encodes 16 E2M1 codes and stores
+// 8 code bytes + 1 scale byte at slot = page * PS + position. Threads of a warp cover consecutive blocks, so global
+// reads are 1 KiB per warp and the code stores 256 contiguous bytes per (token, head, side) row.
+//
+// Bit-exactness: the result must equal the reference's PyTorch quantiser (kv_fp4_ref.py:159-186 `quantize_rows`,
+// rules at kv_fp4_ref.py:15-25) byte for byte. Every arithmetic step is therefore a single IEEE fp32 operation issued
+// through an explicit intrinsic (__fdiv_rn, __fmul_rn, __fsub_rn, __fadd_rn): no contraction into FMA, no fast-math.
+// The squared error is summed sequentially over i = 0..15 and a later candidate wins only on a strict "<".
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "hkv_common.cuh"
+
+namespace hkv {
+
+struct WriteParams {
+  const __nv_bfloat16* key;
+  const __nv_bfloat16* val;
+  long long ks0, ks1, vs0, vs1;
+  uint8_t* kd;
+  uint8_t* ksf;
+  uint8_t* vd;
+  uint8_t* vsf;
+  long long dsp, dst, dsh, ssp, sst, ssh;
+  const long long* slots;
+  long long n_slots;
+  const float* gk;
+  const float* gv;
+  int PS, KVH;
+};
+
+// e4m3fn of x >= 0, round to nearest even, saturating at 448 (kv_fp4_ref.py:94-97)
+__device__ __forceinline__ unsigned e4m3_enc(float x) {
+  return (unsigned)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+}
+// value of a non-negative finite e4m3 code 0..126 (exact)
+__device__ __forceinline__ float e4m3_dec(unsigned c) {
+  const unsigned e = (c >> 3) & 15u, m = c & 7u;
+  return e ? __uint_as_float(((e + 120u) << 23) | (m << 20)) : __fmul_rn((float)m, 0.001953125f);
+}
+// E2M1 magnitude code of y >= 0, ties to the even code, saturating (kv_fp4_ref.py:122-130)
+__device__ __forceinline__ unsigned e2m1_mag(float y) {
+  return y <= 0.25f ? 0u : y < 0.75f ? 1u : y <= 1.25f ? 2u : y < 1.75f ? 3u : y <= 2.5f ? 4u : y < 3.5f ? 5u
+       : y <= 5.0f ? 6u : 7u;
+}
+__device__ __forceinline__ float e2m1_val(unsigned m) {
+  const unsigned e = (m >> 1) & 3u, l = m & 1u;
+  return e ? __uint_as_float(((e + 126u) << 23) | (l << 22)) : (l ? 0.5f : 0.0f);
+}
+__device__ __forceinline__ unsigned mag_of(float ax, float s) { return s > 0.0f ? e2m1_mag(__fdiv_rn(ax, s)) : 0u; }
+
+// sequential squared error of the block under effective scale s (kv_fp4_ref.py:148-156)
+__device__ __forceinline__ float block_sse(const float (&ax)[16], float s) {
+  float acc = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float d = __fsub_rn(__fmul_rn(e2m1_val(mag_of(ax[i], s)), s), ax[i]);
+    const float sq = __fmul_rn(d, d);
+    acc = i == 0 ? sq : __fadd_rn(acc, sq);
+  }
+  return acc;
+}
+
+template <int D, int SEARCH>
+__global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
+  constexpr int NB = D / 16;                      // blocks per row
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int per_tok = 2 * p.KVH * NB;
+  const long long t = gid / per_tok;
+  if (t >= p.n_slots) return;
+  const int rem = (int)(gid - t * per_tok);
+  const int side = rem / (p.KVH * NB);
+  const int hb = rem - side * (p.KVH * NB);
+  const int h = hb / NB, blk = hb - h * NB;
+  const long long slot = p.slots[t];
+  if (slot < 0) return;
+
+  const __nv_bfloat16* src = side ? p.val + t * p.vs0 + h * p.vs1 : p.key + t * p.ks0 + h * p.ks1;
+  const uint4 w0 = *reinterpret_cast<const uint4*>(src + blk * 16);
+  const uint4 w1 = *reinterpret_cast<const uint4*>(src + blk * 16 + 8);
+  const uint32_t ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+  float ax[16];
+  unsigned neg = 0;                               // bit i: x_i < 0 (false for -0.0, as in the reference)
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float lo = __uint_as_float(ws[i] << 16), hi = __uint_as_float(ws[i] & 0xffff0000u);
+    neg |= (lo < 0.0f ? 1u : 0u) << (2 * i);
+    neg |= (hi < 0.0f ? 1u : 0u) << (2 * i + 1);
+    ax[2 * i] = fabsf(lo);
+    ax[2 * i + 1] = fabsf(hi);
+    amax = fmaxf(amax, fmaxf(ax[2 * i], ax[2 * i + 1]));
+  }
+  const float g = side ? p.gv[h] : p.gk[h];
+  unsigned cb = e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 6.0f)));
+  if (SEARCH) {
+    const int c0 = (int)cb;
+    const unsigned cand[3] = {(unsigned)min(c0 + 1, 126), (unsigned)max(c0 - 1, 0),
+                              e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 4.0f)))};
+    float best = block_sse(ax, __fmul_rn(e4m3_dec(cb), g));
+#pragma unroll 1
+    for (int k = 0; k < 3; ++k) {
+      const float e = block_sse(ax, __fmul_rn(e4m3_dec(cand[k]), g));
+      if (e < best) {
+        best = e;
+        cb = cand[k];
+      }
+    }
+  }
+  const float s = __fmul_rn(e4m3_dec(cb), g);
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    lo |= (mag_of(ax[i], s) | (((neg >> i) & 1u) << 3)) << (4 * i);
+    hi |= (mag_of(ax[8 + i], s) | (((neg >> (8 + i)) & 1u) << 3)) << (4 * i);
+  }
+  const long long page = slot / p.PS, pos = slot - page * p.PS;
+  uint8_t* dd = (side ? p.vd : p.kd) + page * p.dsp + pos * p.dst + h * p.dsh + blk * 8;
+  uint8_t* ds = (side ? p.vsf : p.ksf) + page * p.ssp + pos * p.sst + h * p.ssh + blk;
+  *reinterpret_cast<uint2*>(dd) = make_uint2(lo, hi);
+  *ds = (uint8_t)cb;
+}
+
+static int g_last_cuda_error = 0;
+
+}  // namespace hkv
+
+extern "C" int hkv_last_cuda_error(void) { return hkv::g_last_cuda_error; }
+
+extern "C" int hkv_version(void) { return 100; }
+
+extern "C" const char* hkv_error_string(int code) {
+  switch (code) {
+    case HKV_OK: return "ok";
+    case HKV_ERR_NULL: return "a required pointer is null";
+    case HKV_ERR_ALIGN: return "a pointer or stride misses the required alignment";
+    case HKV_ERR_UNSUPPORTED: return "unsupported head_dim, group size, page size, query length or layout";
+    case HKV_ERR_SPLITS: return "more than 64 splits";
+    case HKV_ERR_WORKSPACE: return "workspace too small";
+    case HKV_ERR_RANGE: return "a size is negative or too large";
+    case HKV_ERR_CUDA: return "a CUDA runtime call failed";
+    case HKV_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel ran out";
+    default: return "unknown error code";
+  }
+}
+
+namespace hkv {
+int record_cuda(cudaError_t e) {
+  if (e == cudaSuccess) return HKV_OK;
+  g_last_cuda_error = (int)e;
+  return HKV_ERR_CUDA;
+}
+}  // namespace hkv
+
+extern "C" int hkv_write(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1,
+                         void* kd, void* ksf, void* vd, void* vsf, const int64_t strides[6], int PS,
+                         const int64_t* slots, int64_t n_slots, const float* gk, const float* gv, int KVH, int D,
+                         int search, void* stream) {
+  using namespace hkv;
+  if (n_slots < 0) return HKV_ERR_RANGE;
+  if (n_slots == 0) return HKV_OK;
+  if (!key || !val || !kd || !ksf || !vd || !vsf || !strides || !slots || !gk || !gv) return HKV_ERR_NULL;
+  if (D != 128 && D != 256) return HKV_ERR_UNSUPPORTED;
+  if (KVH < 1 || KVH > 1024 || PS < 1) return HKV_ERR_UNSUPPORTED;
+  // 16-byte row loads of bf16 and 8-byte code stores
+  if (((uintptr_t)key | (uintptr_t)val) & 15) return HKV_ERR_ALIGN;
+  if ((ks0 | ks1 | vs0 | vs1) & 7) return HKV_ERR_ALIGN;
+  if (((uintptr_t)kd | (uintptr_t)vd) & 7) return HKV_ERR_ALIGN;
+  if ((strides[0] | strides[1] | strides[2]) & 7) return HKV_ERR_ALIGN;
+  WriteParams p;
+  p.key = (const __nv_bfloat16*)key;
+  p.val = (const __nv_bfloat16*)val;
+  p.ks0 = ks0; p.ks1 = ks1; p.vs0 = vs0; p.vs1 = vs1;
+  p.kd = (uint8_t*)kd; p.ksf = (uint8_t*)ksf; p.vd = (uint8_t*)vd; p.vsf = (uint8_t*)vsf;
+  p.dsp = strides[0]; p.dst = strides[1]; p.dsh = strides[2];
+  p.ssp = strides[3]; p.sst = strides[4]; p.ssh = strides[5];
+  p.slots = (const long long*)slots;
+  p.n_slots = n_slots;
+  p.gk = gk; p.gv = gv; p.PS = PS; p.KVH = KVH;
+  const long long threads = n_slots * 2 * KVH * (D / 16);
+  const long long blocks = (threads + 255) / 256;
+  if (blocks > 0x7fffffffll) return HKV_ERR_RANGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (D == 128) {
+    if (search) write_kernel<128, 1><<<(unsigned)blocks, 256, 0, st>>>(p);
+    else write_kernel<128, 0><<<(unsigned)blocks, 256, 0, st>>>(p);
+  } else {
+    if (search) write_kernel<256, 1><<<(unsigned)blocks, 256, 0, st>>>(p);
+    else write_kernel<256, 0><<<(unsigned)blocks, 256, 0, st>>>(p);
+  }
+  return record_cuda(cudaGetLastError());
+}

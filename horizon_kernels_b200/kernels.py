@@ -1,0 +1,130 @@
+"""Host wrappers of the three CUDA kernels, with the call signatures of the reference's serving module
+(nvidia-sm120/horizon_kvfp4/kernels/kv_fp4_serving.py): `write`, `decode_ragged`, `flat_views`, `plan_splits`.
+
+The wrappers only marshal pointers, sizes and the current CUDA stream into the C ABI (include/hkv.h). They allocate
+nothing and never synchronise, so calls can be captured in a CUDA graph. There is no CPU or PyTorch fallback."""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from .layout import flat_views  # noqa: F401  (re-exported: part of the reference's API)
+
+LOG2E = 1.4426950408889634
+_SMS = {}
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr())
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if not t.is_cuda:
+            raise RuntimeError("hkv kernels need CUDA tensors: there is no CPU path")
+
+
+def num_sms(device=None) -> int:
+    d = torch.cuda.current_device() if device is None else torch.device(device).index
+    if d not in _SMS:
+        _SMS[d] = torch.cuda.get_device_properties(d).multi_processor_count
+    return _SMS[d]
+
+
+def plan_splits(B: int, KVH: int, ctas_per_sm: int = 4, max_splits: int = 64, sms: int = None) -> int:
+    """splits per (request, kv head); depends on the batch size only, so it is safe under CUDA graphs
+    (reference: kv_fp4_serving.py:889-891)"""
+    sms = num_sms() if sms is None else sms
+    return max(1, min(max_splits, sms * ctas_per_sm // max(1, B * KVH)))
+
+
+def workspace_bytes(B: int, KVH: int, G: int, D: int, qlmax: int = 1) -> int:
+    n = int(_lib.load().hkv_decode_workspace_bytes(B, KVH, G, D, qlmax))
+    if n == 0:
+        raise _lib.HkvError(-3, "hkv_decode_workspace_bytes")
+    return n
+
+
+def alloc_workspace(B: int, KVH: int, G: int, D: int, qlmax: int = 1, device="cuda") -> torch.Tensor:
+    """zeroed uint8 workspace for decode batches of up to B requests; allocate once, outside graph capture
+    (reference: backend.py:263-277)"""
+    with torch.cuda.device(device):
+        return torch.zeros(workspace_bytes(B, KVH, G, D, qlmax), dtype=torch.uint8, device=device)
+
+
+def write(key, value, flat, strides, PS, slot_mapping, gk, gv, search=True, signs=None, k8=False):
+    """key / value (NT, KVH, D) bf16 views (any token / head strides, last dim contiguous); slot_mapping (NSL,) int64,
+    slot < 0 skipped, tokens beyond NSL untouched; flat / strides from flat_views; gk / gv (KVH,) fp32.
+    Bit-exact to the reference's write_reference (kv_fp4_ref.py:233-245). Signature of kv_fp4_serving.py:994."""
+    if signs is not None or k8:
+        raise NotImplementedError("key rotation and the K8V4 slot are not built")
+    _need_cuda(key, value, slot_mapping, gk, gv, *flat)
+    if key.dtype != torch.bfloat16 or value.dtype != torch.bfloat16:
+        raise TypeError("key / value must be bf16")
+    if key.stride(-1) != 1 or value.stride(-1) != 1:
+        raise ValueError("key / value need a contiguous last dimension")
+    if slot_mapping.dtype != torch.int64 or not slot_mapping.is_contiguous():
+        raise TypeError("slot_mapping must be contiguous int64")
+    if slot_mapping.shape[0] > key.shape[0]:
+        raise ValueError("more slots than tokens")
+    KVH, D = key.shape[1], key.shape[2]
+    kd, ksf, vd, vsf = flat
+    st = (C.c_int64 * 6)(*strides)
+    with torch.cuda.device(key.device):
+        rc = _lib.load().hkv_write(_ptr(key), _ptr(value), key.stride(0), key.stride(1), value.stride(0),
+                                   value.stride(1), _ptr(kd), _ptr(ksf), _ptr(vd), _ptr(vsf), st, int(PS),
+                                   _ptr(slot_mapping), slot_mapping.shape[0], _ptr(gk), _ptr(gv), KVH, D,
+                                   int(bool(search)), _stream())
+    _lib.check(rc, "hkv_write")
+
+
+def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_loc, bmm1_scale, bmm2_scale, gk, gv,
+                  qlmax, out, workspace, splits=None, nst=None, ncw=None, min_chunk=None, tw=None, signs=None,
+                  k8=False):
+    """query (NT, HQ, D) bf16 contiguous; block_tables (B, MP) int32; seq_lens (B,) int32; query_start_loc (B + 1,)
+    int32; out (>= NT, HQ, D) bf16, rows of requests without (or with more than qlmax) query tokens are left
+    untouched; workspace from alloc_workspace. out = softmax(q k^T * bmm1_scale * gk) v * gv * bmm2_scale.
+    `splits` bounds the number of stream partitions to B * KVH * splits; the tuning arguments of the reference
+    (nst, ncw, min_chunk, tw) are accepted and ignored. Signature of kv_fp4_serving.py:894-895."""
+    if signs is not None or k8:
+        raise NotImplementedError("key rotation and the K8V4 slot are not built")
+    _need_cuda(query, block_tables, seq_lens, query_start_loc, gk, gv, out, workspace, *flat)
+    if query.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise TypeError("query / out must be bf16")
+    if not query.is_contiguous() or not out.is_contiguous():
+        raise ValueError("query / out must be contiguous")
+    for t in (block_tables, seq_lens, query_start_loc):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise TypeError("block_tables / seq_lens / query_start_loc must be contiguous int32")
+    B, MP = block_tables.shape
+    KVH = gk.shape[0]
+    HQ, D = query.shape[1], query.shape[2]
+    G = HQ // KVH
+    S = 0 if splits is None else int(splits)
+    kd, ksf, vd, vsf = flat
+    st = (C.c_int64 * 6)(*strides)
+    wsb = workspace.numel() * workspace.element_size()
+    L = _lib.load()
+    with torch.cuda.device(query.device):
+        s = _stream()
+        rc = L.hkv_decode(_ptr(query), _ptr(kd), _ptr(ksf), _ptr(vd), _ptr(vsf), st, int(PS), _ptr(block_tables), MP,
+                          _ptr(seq_lens), _ptr(query_start_loc), B, KVH, G, D, int(qlmax), float(bmm1_scale),
+                          float(bmm2_scale), _ptr(gk), _ptr(gv), _ptr(workspace), wsb, S, _ptr(out), s)
+        _lib.check(rc, "hkv_decode")
+        rc = L.hkv_combine(_ptr(workspace), wsb, _ptr(query_start_loc), B, KVH, G, D, int(qlmax), float(bmm2_scale),
+                           _ptr(out), s)
+        _lib.check(rc, "hkv_combine")
+    return out
+
+
+def workspace_status(workspace) -> int:
+    """device status word of the last launches (0 = ok); synchronises, for tests and debugging"""
+    st = C.c_int(0)
+    with torch.cuda.device(workspace.device):
+        rc = _lib.load().hkv_workspace_status(_ptr(workspace), C.byref(st), _stream())
+    _lib.check(rc, "hkv_workspace_status")
+    return int(st.value)

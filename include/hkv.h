@@ -1,0 +1,103 @@
+/*
+ * hkv: NVFP4 paged KV-cache kernels for NVIDIA B200 (sm_100a) behind a plain C ABI.
+ *
+ * Cache format (per token, kv head and side K or V; head_dim D in {128, 256}):
+ *   data : D/2 bytes of E2M1 codes, element 2j in the low nibble of byte j
+ *   sf   : D/16 bytes, one E4M3 scale per 16 consecutive elements
+ *   g    : one fp32 global scale per (kv head, side), passed by the caller (gk, gv)
+ *   value = e2m1(code) * e4m3(sf) * g
+ * The four parts of a cache (K data, K scales, V data, V scales) are described the way the reference's kernels take
+ * them: a base pointer per part plus byte strides of a [page, position, head, byte] view,
+ *   strides = {data page, data position, data head, scale page, scale position, scale head}
+ * (reference: nvidia-sm120/horizon_kvfp4/kernels/kv_fp4_serving.py:873-886 `flat_views`, :37 `Strides`).
+ *
+ * Every function returns HKV_OK or a negative error code, launches on the given CUDA stream, never allocates, never
+ * synchronises and never reads device data on the host, so a sequence of calls can be captured in a CUDA graph.
+ * Host-detectable misuse (null or misaligned pointers, unsupported head_dim / group size / page size, a workspace that
+ * is too small) is rejected before anything is launched.
+ */
+#ifndef HKV_H_
+#define HKV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HKV_OK 0
+#define HKV_ERR_NULL (-1)         /* a required pointer is null */
+#define HKV_ERR_ALIGN (-2)        /* a pointer or stride misses the alignment the kernels need */
+#define HKV_ERR_UNSUPPORTED (-3)  /* head_dim, group size, page size, query length or layout outside the supported set */
+#define HKV_ERR_SPLITS (-4)       /* more than 64 splits requested */
+#define HKV_ERR_WORKSPACE (-5)    /* workspace too small */
+#define HKV_ERR_RANGE (-6)        /* a size is negative or too large */
+#define HKV_ERR_CUDA (-7)         /* a CUDA runtime call failed; hkv_last_cuda_error() has the code */
+#define HKV_ERR_DEVICE_WAIT (-8)  /* a bounded wait inside a kernel ran out (read back by hkv_workspace_status) */
+
+/* library version (major * 10000 + minor * 100 + patch) and a text for an error code */
+int hkv_version(void);
+const char* hkv_error_string(int code);
+int hkv_last_cuda_error(void);
+
+/*
+ * Quantize-on-write: bf16 K / V rows -> E2M1 codes + E4M3 block scales, scattered to slot = page * PS + position.
+ * Replaces `write` / `hz4::write_task` (kv_fp4_serving.py:994-1005, :618-700) and is bit-exact to `write_reference`
+ * (kv_fp4_ref.py:233-245) without the optional key rotation.
+ *   key, val : bf16, logical (n_tokens >= n_slots, KVH, D); element strides ks0/vs0 (token) and ks1/vs1 (head), last
+ *              dimension contiguous and 16-byte aligned rows
+ *   slots    : int64[n_slots]; a negative slot skips the token
+ *   gk, gv   : fp32[KVH] global scales
+ *   search   : 1 = choose the block scale among 4 candidates by squared error (the reference's default), 0 = plain
+ */
+int hkv_write(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1, void* kd,
+              void* ksf, void* vd, void* vsf, const int64_t strides[6], int PS, const int64_t* slots, int64_t n_slots,
+              const float* gk, const float* gv, int KVH, int D, int search, void* stream);
+
+/*
+ * Workspace for hkv_decode + hkv_combine on the current device: bytes needed for a batch of up to B requests.
+ * The size depends on the device (number of SMs) and on (B, KVH, G, D, qlmax) only, never on context lengths, so one
+ * allocation made outside graph capture serves every step. Replaces the sizing loop at backend.py:263-277.
+ * Returns 0 for unsupported arguments.
+ */
+size_t hkv_decode_workspace_bytes(int B, int KVH, int G, int D, int qlmax);
+
+/*
+ * Paged split-K flash-decoding over the FP4 cache. Replaces `decode_ragged` / `hz4::attn_task_rg`
+ * (kv_fp4_serving.py:894-915, :99-511):
+ *   out[qsl[b] + t, h*G + g, :] = softmax_j(q . k_j * sm_scale * gk[h]) @ v_j * gv[h] * v_scale,  j < L_b - ql_b + t + 1
+ * The concatenated (request, kv head) token streams are cut into equal partitions, one per resident CTA; a sequence
+ * that lies inside one partition is written to `out` directly, the others leave normalised fp32 partials and
+ * log2-sum-exp values in the workspace for hkv_combine. `splits` (1..64, or 0 = automatic) bounds the number of
+ * partitions to B * KVH * splits like the reference's grid (kv_fp4_serving.py:889-891); it depends on the batch size
+ * only.
+ *   q            : bf16 (n_tokens, KVH*G, D) contiguous
+ *   block_tables : int32 (B, MP); seq_lens int32 (B); query_start_loc int32 (B + 1)
+ *   requests with 0 or more than qlmax query tokens are skipped and their output rows left untouched
+ *   out          : bf16 (>= n_tokens, KVH*G, D) contiguous
+ */
+int hkv_decode(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
+               const int64_t strides[6], int PS, const int32_t* block_tables, int MP, const int32_t* seq_lens,
+               const int32_t* query_start_loc, int B, int KVH, int G, int D, int qlmax, float sm_scale, float v_scale,
+               const float* gk, const float* gv, void* workspace, size_t workspace_bytes, int splits, void* out,
+               void* stream);
+
+/*
+ * Log-sum-exp merge of the partials hkv_decode left in the workspace, in partition order (deterministic).
+ * Replaces `hz4::combine_rg` (kv_fp4_serving.py:518-558). Must follow hkv_decode on the same stream with the same
+ * (B, KVH, G, D, qlmax, v_scale, out).
+ */
+int hkv_combine(const void* workspace, size_t workspace_bytes, const int32_t* query_start_loc, int B, int KVH, int G,
+                int D, int qlmax, float v_scale, void* out, void* stream);
+
+/*
+ * Copies the workspace's device status word to *status (HKV_OK or HKV_ERR_DEVICE_WAIT) and clears it. Synchronises the
+ * stream: a debugging aid, not for the hot path.
+ */
+int hkv_workspace_status(void* workspace, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HKV_H_ */

@@ -1,0 +1,190 @@
+"""Lane-level CPU emulation of one 16-token step of the CUDA decode kernel (horizon_kernels_b200/csrc/hkv_decode.cu):
+the documented register layout of mma.m16n8k16, the kernel's choice of which cache bytes every lane dequantises, the
+token permutation of the score tiles and the nibble re-pairing of the value tile. The emulated scores and outputs must
+equal a direct dequantise-and-multiply of the same bytes, and two deliberately wrong mappings must fail.
+(The reference pins its own kernel the same way: scripts/kernels/kvfp4/test_kvfp4_v2_cpu.py V4 in the reference tree.)
+"""
+import numpy as np
+import pytest
+
+import synth
+from oracle import kvfp4 as O
+
+
+def mma_m16n8k16(a_regs, b_regs, c_regs):
+    """a_regs (32, 4, 2), b_regs (32, 2, 2), c_regs (32, 4): registers of f16 pairs per lane -> new c_regs"""
+    A = np.zeros((16, 16))
+    Bm = np.zeros((16, 8))
+    for lane in range(32):
+        g, c = lane >> 2, lane & 3
+        for i in range(4):
+            row = g + 8 * (i & 1)
+            col = 2 * c + 8 * (i >> 1)
+            A[row, col], A[row, col + 1] = a_regs[lane, i]
+        for i in range(2):
+            k = 2 * c + 8 * i
+            Bm[k, g], Bm[k + 1, g] = b_regs[lane, i]
+    Cm = A @ Bm
+    out = c_regs.copy()
+    for lane in range(32):
+        g, c = lane >> 2, lane & 3
+        out[lane, 0] += Cm[g, 2 * c]
+        out[lane, 1] += Cm[g, 2 * c + 1]
+        out[lane, 2] += Cm[g + 8, 2 * c]
+        out[lane, 3] += Cm[g + 8, 2 * c + 1]
+    return out
+
+
+E2M1 = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6])
+
+
+def cvt_byte(b):
+    """cvt.rn.f16x2.e2m1x2: low nibble -> low half"""
+    return E2M1[b & 15], E2M1[b >> 4]
+
+
+class Geo:
+    def __init__(self, D, layout):
+        self.D, self.layout = D, layout
+        self.SD, self.SS = D // 2, D // 16
+        self.SLOT = self.SD + self.SS
+        self.ROW = self.SLOT if layout == 0 else self.SD
+        self.SF_BASE = self.SD if layout == 0 else 16 * self.SD
+        self.SF_ROW = self.SLOT if layout == 0 else self.SS
+        self.KS, self.NBL, self.NH = D // 16, D // 64, D // 128
+
+    def tok(self, t, n):
+        return 2 * n + t if (self.D == 128 and self.layout == 0) else n + 8 * t
+
+    def kblk(self, c, u):
+        return c + 4 * u if self.D == 128 else 2 * c + (u & 1) + 8 * (u >> 1)
+
+
+def make_tile(seed, geo):
+    """one (head, side) tile of 16 tokens in the kernel's shared-memory byte order, plus its dequantised matrix"""
+    x = (synth.normal(seed, (16, geo.D)) * 3).astype(np.float32)
+    data, sf = O.quantize_rows(x, 1.0)
+    deq = O.dequantize_rows(data, sf)
+    tile = np.zeros(16 * geo.SLOT, np.uint8)
+    for r in range(16):
+        tile[r * geo.ROW:r * geo.ROW + geo.SD] = data[r]
+        tile[geo.SF_BASE + r * geo.SF_ROW:geo.SF_BASE + r * geo.SF_ROW + geo.SS] = sf[r]
+    return tile, deq
+
+
+def emulate_unit(geo, kt, vt, q, wrong=None):
+    """q (8, D) float. Returns S (8 rows, 16 tokens) and O (8 rows, D) accumulated with P = S (no softmax), exactly as
+    the kernel's fragments would hold them."""
+    D = geo.D
+    sf_val = O.e4m3_decode(np.arange(256, dtype=np.uint8))
+    # query fragments qa[lane][kstep][2 regs][2 halves]
+    qa = np.zeros((32, geo.KS, 2, 2))
+    for lane in range(32):
+        g, c = lane >> 2, lane & 3
+        for u in range(geo.NBL):
+            ch0 = 16 * geo.kblk(c, u)
+            for i in range(8):
+                qa[lane, 4 * u + (i >> 1), i & 1] = q[g, ch0 + 2 * i], q[g, ch0 + 2 * i + 1]
+    s = [np.zeros((32, 4)), np.zeros((32, 4))]
+    for u in range(geo.NBL):
+        e = np.zeros((2, 32, 8, 2))                  # [tile][lane][byte of the block][half]
+        for lane in range(32):
+            g, c = lane >> 2, lane & 3
+            kb = geo.kblk(c, u)
+            if wrong == "kblock" and u == 0:
+                kb = geo.kblk((c + 1) % 4, u)
+            for t in range(2):
+                r = geo.tok(t, g)
+                scale = sf_val[kt[geo.SF_BASE + r * geo.SF_ROW + kb]]
+                for by in range(8):
+                    lo, hi = cvt_byte(int(kt[r * geo.ROW + 8 * kb + by]))
+                    e[t, lane, by] = lo * scale, hi * scale
+        for v in range(4):
+            a = np.zeros((32, 4, 2))
+            a[:, 0] = qa[:, 4 * u + v, 0]
+            a[:, 2] = qa[:, 4 * u + v, 1]
+            for t in range(2):
+                b = np.stack([e[t, :, 2 * v], e[t, :, 2 * v + 1]], axis=1)
+                s[t] = mma_m16n8k16(a, b, s[t])
+    S = np.zeros((8, 16))
+    pb = np.zeros((32, 2, 2))
+    for lane in range(32):
+        g, c = lane >> 2, lane & 3
+        toks = (geo.tok(0, 2 * c), geo.tok(0, 2 * c + 1), geo.tok(1, 2 * c), geo.tok(1, 2 * c + 1))
+        vals = (s[0][lane, 0], s[0][lane, 1], s[1][lane, 0], s[1][lane, 1])
+        for tk, x in zip(toks, vals):
+            S[g, tk] = x
+        pb[lane, 0] = vals[0], vals[1]
+        pb[lane, 1] = vals[2], vals[3]
+    o = np.zeros((geo.KS, 32, 4))
+    for hf in range(geo.NH):
+        for jj in range(8):
+            a = np.zeros((32, 4, 2))
+            for lane in range(32):
+                g, c = lane >> 2, lane & 3
+                vb = g + 8 * hf
+                toks = [geo.tok(0, 2 * c), geo.tok(0, 2 * c + 1), geo.tok(1, 2 * c), geo.tok(1, 2 * c + 1)]
+                if wrong == "vtokens":
+                    toks[0], toks[1] = toks[1], toks[0]
+                w = [vt[t * geo.ROW + 8 * vb:t * geo.ROW + 8 * vb + 8].astype(np.int64) for t in toks]
+                f = [sf_val[vt[geo.SF_BASE + t * geo.SF_ROW + vb]] for t in toks]
+                for pair in range(2):
+                    w0, w1 = w[2 * pair], w[2 * pair + 1]
+                    xe = (w0 & 15) | ((w1 & 15) << 4)         # even channels: low nibble = first token of the pair
+                    xo = (w0 >> 4) | (w1 & 0xF0)              # odd channels
+                    lo, hi = cvt_byte(int(xe[jj]))
+                    a[lane, 2 * pair] = lo * f[2 * pair], hi * f[2 * pair + 1]
+                    lo, hi = cvt_byte(int(xo[jj]))
+                    a[lane, 2 * pair + 1] = lo * f[2 * pair], hi * f[2 * pair + 1]
+            o[8 * hf + jj] = mma_m16n8k16(a, pb, o[8 * hf + jj])
+    Om = np.zeros((8, D))
+    for lane in range(32):
+        g, c = lane >> 2, lane & 3
+        for hf in range(geo.NH):
+            for jj in range(8):
+                ch = 16 * (g + 8 * hf) + 2 * jj
+                a = o[8 * hf + jj][lane]
+                Om[2 * c, ch], Om[2 * c, ch + 1] = a[0], a[2]
+                Om[2 * c + 1, ch], Om[2 * c + 1, ch + 1] = a[1], a[3]
+    return S, Om
+
+
+@pytest.mark.parametrize("D,layout", [(128, 0), (128, 1), (256, 0), (256, 1)])
+def test_unit_mapping(D, layout):
+    geo = Geo(D, layout)
+    kt, kdeq = make_tile(10 + D + layout, geo)
+    vt, vdeq = make_tile(20 + D + layout, geo)
+    q = synth.bf16_bits_to_f32(synth.to_bf16_bits(synth.normal(30 + D, (8, D)))).astype(np.float64)
+    S, Om = emulate_unit(geo, kt, vt, q)
+    S_ref = q @ kdeq.T
+    assert np.abs(S - S_ref).max() <= 1e-9 * np.abs(S_ref).max()
+    O_ref = S_ref @ vdeq
+    assert np.abs(Om - O_ref).max() <= 1e-9 * np.abs(O_ref).max()
+
+
+@pytest.mark.parametrize("wrong", ["kblock", "vtokens"])
+def test_negative_controls(wrong):
+    geo = Geo(128, 0)
+    kt, kdeq = make_tile(41, geo)
+    vt, vdeq = make_tile(42, geo)
+    q = synth.normal(43, (8, 128))
+    S, Om = emulate_unit(geo, kt, vt, q, wrong=wrong)
+    S_ref = q @ kdeq.T
+    O_ref = S_ref @ vdeq
+    err = max(np.abs(S - S_ref).max() / np.abs(S_ref).max(), np.abs(Om - O_ref).max() / np.abs(O_ref).max())
+    assert err > 0.05
+
+
+def test_value_loads_hit_distinct_banks():
+    """the 64-bit value loads of a half warp (lanes 0-15) touch 32 distinct 4-byte banks in the slot layout"""
+    for D in (128, 256):
+        geo = Geo(D, 0)
+        for which in range(4):
+            for half in range(2):
+                banks = []
+                for lane in range(16 * half, 16 * half + 16):
+                    g, c = lane >> 2, lane & 3
+                    t = (geo.tok(0, 2 * c), geo.tok(0, 2 * c + 1), geo.tok(1, 2 * c), geo.tok(1, 2 * c + 1))[which]
+                    addr = t * geo.ROW + 8 * g
+                    banks += [(addr // 4) % 32, (addr // 4 + 1) % 32]
+                assert len(set(banks)) == 32, (D, which, half)

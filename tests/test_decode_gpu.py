@@ -1,0 +1,164 @@
+"""GPU parity of the split-K decode + combine kernels, through the C ABI, against the reference's fp64 attention over
+the same dequantised cache (golden fixtures) and against the CPU oracle. Tolerances are the task's: max-abs 2e-2,
+mean-abs 2e-3, and the reference's own gate, relative L2 2.5e-3 (scripts/kernels/kvfp4/test_kvfp4_gpu.py:51).
+Mirrors the reference's decode gates G3 / G3v2 / S1: partial pages, garbage bytes (0x7F = NaN as E4M3) outside the
+written slots, non-unit global scales, a padded output buffer, determinism, NaN-poisoned CUDA-graph replay."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import synth
+from cases import (Cache, assert_close, bf16_tensor, build_decode_case, errors, gpu_decode, oracle_decode)
+from horizon_kernels_b200 import kernels as K
+from horizon_kernels_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", ["g4", "g8"])
+def test_attention_golden(golden_dir, name):
+    """the reference's own attention_reference output on a cache the reference wrote"""
+    z = np.load(os.path.join(golden_dir, "attention.npz"))
+    KVH, G, D, PS, QL, NP = (int(v) for v in z[f"{name}_geom"])
+    cache = Cache(NP, PS, KVH, D, "region")
+    cache.load(z[f"{name}_cache"])
+    sm, vs = (float(v) for v in z[f"{name}_sm"])
+    c = dict(cache=cache, q=z[f"{name}_q"], bt=z[f"{name}_bt"], seq_lens=z[f"{name}_seq_lens"], qsl=z[f"{name}_qsl"],
+             gk=z[f"{name}_gk"], gv=z[f"{name}_gv"], KVH=KVH, G=G, D=D, sm=sm)
+    out, ws = gpu_decode(c, v_scale=vs)
+    assert K.workspace_status(ws) == 0
+    assert_close(out, z[f"{name}_ref"], name)
+
+
+def test_config0_golden(golden_dir):
+    """batch 4, 32 / 8 heads, head_dim 128, 2048 tokens each, 512 pages: cache bytes equal to the reference's
+    (sha256) and attention within tolerance of the reference's fp64 output"""
+    import hashlib
+    from test_oracle import config0_inputs
+    z = np.load(os.path.join(golden_dir, "config0.npz"))
+    c = config0_inputs()
+    cache = Cache(512, 16, 8, 128, "region", fill=0)
+    dev = cache.phys.device
+    K.write(bf16_tensor(c["key"]), bf16_tensor(c["val"]), cache.flat, cache.strides, 16,
+            torch.from_numpy(c["slots"]).to(dev), torch.from_numpy(c["gk"]).to(dev), torch.from_numpy(c["gv"]).to(dev))
+    assert hashlib.sha256(cache.bytes().tobytes()).hexdigest() == str(z["cache_sha256"])
+    c.update(cache=cache, sm=float(z["sm"][0]))
+    out, ws = gpu_decode(c)
+    assert K.workspace_status(ws) == 0
+    mx, mn, rl = assert_close(out, z["ref"], "config0")
+    print("config0 errors", mx, mn, rl)
+
+
+CASES = [
+    # lens, KVH, G, D, PS, layout
+    ([37], 8, 4, 128, 16, "hnd"),
+    ([1, 5, 17, 16, 15, 33], 8, 4, 128, 16, "hnd"),
+    ([1601, 7, 900], 8, 4, 128, 16, "hnd"),
+    ([300, 1000], 8, 8, 128, 16, "hnd"),
+    ([5, 64, 200, 0, 129], 2, 8, 256, 16, "hnd"),
+    ([20000, 7], 2, 8, 256, 16, "hnd"),
+    ([129, 300], 4, 6, 256, 64, "hnd"),
+    ([129, 300, 70], 4, 6, 256, 64, "region"),
+    ([150, 16, 2048], 8, 4, 128, 16, "region"),
+    ([500, 40], 3, 5, 128, 32, "hnd"),
+    ([700], 1, 1, 128, 16, "hnd"),
+]
+
+
+@pytest.mark.parametrize("lens,KVH,G,D,PS,kind", CASES)
+def test_decode_matches_oracle(lens, KVH, G, D, PS, kind):
+    c = build_decode_case(1000 + len(lens) + KVH + G, lens, KVH, G, D, PS, kind=kind, gscale=(0.05, 0.01))
+    ref = oracle_decode(c, v_scale=0.5)
+    NT = c["q"].shape[0]
+    out = torch.full((NT + 3, KVH * G, D), 7.0, dtype=torch.bfloat16, device="cuda")      # padded output buffer
+    out, ws = gpu_decode(c, v_scale=0.5, out=out)
+    assert K.workspace_status(ws) == 0
+    assert_close(out, ref, str(lens))
+    assert (out[NT:] == 7.0).all()                               # rows past the query tokens are untouched
+    out2 = torch.full_like(out, 7.0)
+    gpu_decode(c, v_scale=0.5, out=out2, ws=ws)
+    assert torch.equal(out, out2)                                # deterministic
+    for splits in (1, 2, 64):
+        o3 = torch.full_like(out, 7.0)
+        gpu_decode(c, v_scale=0.5, out=o3, ws=ws, splits=splits)
+        assert_close(o3, ref, f"{lens} splits {splits}")
+
+
+def test_rows_without_query_tokens_are_untouched():
+    """a graph-padding request (0 query tokens) and a prefill row (more than qlmax tokens) are skipped"""
+    lens = [40, 300, 64, 90]
+    c = build_decode_case(2000, lens, 8, 4, 128, 16, ql_list=[1, 0, 1, 3])
+    ref = oracle_decode(c)
+    NT = c["q"].shape[0]
+    out = torch.full((NT, 32, 128), 3.0, dtype=torch.bfloat16, device="cuda")
+    out, _ = gpu_decode(c, out=out, qlmax=1)
+    q0 = c["qsl"]
+    prefill_rows = slice(int(q0[3]), int(q0[4]))
+    assert (out[prefill_rows] == 3.0).all()
+    ref[prefill_rows] = np.nan
+    assert_close(out, ref)
+
+
+def test_two_query_tokens_causal():
+    """MTP-style rows: 2 query tokens with 4 heads per kv head fit the 8-row tile; token t sees L - 2 + t + 1 keys"""
+    c = build_decode_case(2100, [50, 333, 17], 8, 4, 128, 16, ql_list=[2, 2, 1])
+    ref = oracle_decode(c)
+    out, _ = gpu_decode(c, qlmax=2)
+    assert_close(out, ref)
+
+
+def test_long_context_split_and_combine():
+    """64k tokens on one kv head pair: the sequence is cut over every partition and merged by the combine kernel"""
+    c = build_decode_case(2200, [65536], 2, 8, 128, 16)
+    ref = oracle_decode(c)
+    out, ws = gpu_decode(c)
+    assert K.workspace_status(ws) == 0
+    mx, mn, rl = assert_close(out, ref)
+    print("64k errors", mx, mn, rl)
+
+
+def test_graph_replay_with_poisoned_output():
+    c = build_decode_case(2300, [700, 33, 4000, 16], 8, 4, 128, 16)
+    ref = oracle_decode(c)
+    out, ws = gpu_decode(c)
+    torch.cuda.synchronize()
+    first = out.clone()
+    assert_close(first, ref)
+    dev = out.device
+    q = bf16_tensor(c["q"])
+    bt, sl, qsl = (torch.from_numpy(c[k]).to(dev) for k in ("bt", "seq_lens", "qsl"))
+    gk, gv = torch.from_numpy(c["gk"]).to(dev), torch.from_numpy(c["gv"]).to(dev)
+    cache = c["cache"]
+
+    def run():
+        K.decode_ragged(q, cache.flat, cache.strides, cache.PS, bt, sl, qsl, c["sm"], 1.0, gk, gv, 1, out, ws)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        run()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            run()
+    for _ in range(2):
+        out.fill_(float("nan"))
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, first)
+    # the same graph serves other context lengths: shrink two requests on the device and replay
+    sl2 = c["seq_lens"].copy()
+    sl2[0], sl2[2] = 123, 1999
+    sl.copy_(torch.from_numpy(sl2))
+    g.replay()
+    torch.cuda.synchronize()
+    c2 = dict(c, seq_lens=sl2)
+    assert_close(out, oracle_decode(c2))
+
+
+def test_unsupported_shapes_raise():
+    c = build_decode_case(2400, [40], 2, 16, 128, 16, writer="oracle")     # 16 query rows per kv head
+    with pytest.raises(_lib.HkvError):
+        K.alloc_workspace(1, 2, 16, 128, 1)
+    c = build_decode_case(2401, [40], 2, 4, 128, 16, kind="nhd", writer="oracle")
+    with pytest.raises(_lib.HkvError, match="unsupported"):
+        gpu_decode(c)
