@@ -2,6 +2,7 @@
 // narrow-float conversion wrappers. Everything here is inline PTX or plain CUDA; no library calls.
 #pragma once
 
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -57,6 +58,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -70,7 +74,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: returns false when the phase did not complete within kWaitCycles (the caller records the failure and
 // leaves its loop; nothing spins for ever).
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+static __device__ __noinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
@@ -113,6 +117,17 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t x) {
 __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t x) { return *reinterpret_cast<__half2*>(&x); }
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 x) { return *reinterpret_cast<uint32_t*>(&x); }
+// f16x2 product with a scale pair that the compiler can take as a half-broadcast operand
+__device__ __forceinline__ uint32_t hmul2h(uint32_t a, __half2 b) { return h2_as_u32(__hmul2(u32_as_h2(a), b)); }
+// transpose of an 8x8 matrix of 16-bit elements held one row pair per lane (lane l holds row l / 4, columns 2 (l % 4),
+// 2 (l % 4) + 1); used to turn the (token, query row) probabilities into the B operand of the second product
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(a));
   return r;
 }
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {

@@ -68,8 +68,9 @@ struct Geo {
   static constexpr int KS = D / 16;                    // k-steps of Q K^T == mma tiles of P V
   static constexpr int NBL = D / 64;                   // 16-channel blocks of one key row held by one lane
   static constexpr int NH = D / 128;                   // 16-channel blocks of one value row held by one lane
-  // token handled by column n of score tile t (chosen so that the value loads of a warp hit distinct banks)
-  __device__ static constexpr int tok(int t, int n) { return (D == 128 && LAYOUT == 0) ? 2 * n + t : n + 8 * t; }
+  // token (row of the stage) handled by row i of the 16-row score tile (chosen so that the value loads of a warp hit
+  // distinct shared-memory banks)
+  __device__ static constexpr int tok(int i) { return (D == 128 && LAYOUT == 0) ? 2 * (i & 7) + (i >> 3) : i; }
   // 16-channel block of a key row held by lane column c as its u-th block
   __device__ static constexpr int kblk(int c, int u) { return D == 128 ? c + 4 * u : 2 * c + (u & 1) + 8 * (u >> 1); }
 };
@@ -101,7 +102,7 @@ struct Smem {
 };
 
 template <int D, int LAYOUT, int NS>
-__global__ void __launch_bounds__(NTHREADS) decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(const DecodeParams p) {
   using Gm = Geo<D, LAYOUT>;
   using Sm = Smem<D, LAYOUT, NS>;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_kernel(const DecodeParams p) 
     base0 = coarse[lo_g] + __shfl_sync(0xffffffffu, incl - u, j);
   }
 
-  // ---- fetch side: walks this warp's units (local index k = w, w + TG, ..) and issues their bulk copies
+  // ---- compute-side walker over the pieces of the partition (identical in every warp)
   struct Walker {
     int b, h, blk;
     long long seq0;                                // stream position of block 0 of (b, h)
@@ -214,56 +215,102 @@ __global__ void __launch_bounds__(NTHREADS) decode_kernel(const DecodeParams p) 
     }
     wk.blk = (int)(pos - wk.seq0);
   };
-  Walker fw, cw;
-  fw.b = b0;
-  fw.r = load_req(p, b0);
-  fw.h = (int)((lo - (long long)base0 * KVH) / fw.r.U);
-  fw.seq0 = (long long)base0 * KVH + (long long)fw.h * fw.r.U;
-  fw.blk = 0;
-  cw = fw;
+  Walker cw;
+  cw.b = b0;
+  cw.r = load_req(p, b0);
+  cw.h = (int)((lo - (long long)base0 * KVH) / cw.r.U);
+  cw.seq0 = (long long)base0 * KVH + (long long)cw.h * cw.r.U;
+  cw.blk = 0;
 
+  // ---- fetch side: this warp's units are the partition-local indices w, w + TG, ..; the cursor below runs NS units
+  // ahead of the compute loop. The common case (next unit in the same sequence, its page id already in the warp's
+  // 32-entry window) costs a shuffle, one 64-bit multiply-add and the copy instructions of one lane.
   const int n_my = n_units > w ? (n_units - w + TG - 1) / TG : 0;
   uint8_t* my_ring = ring + w * NS * Gm::STAGE;
   uint64_t* my_bars = bars + w * NS;
-  int pg_b = -1, pg_h = -1, pg_blk0 = 0;            // block-table prefetch window of the fetch walker
-  int pg = 0;
+  int f_b = cw.b, f_h = cw.h, f_U = cw.r.U, f_L = cw.r.L;
+  int f_blk = w + (int)(lo - cw.seq0);              // block (inside the cursor's sequence) of the next unit; may run past
+  int f_fast_end = 0;                               // blocks below this bound take the fast path
+  int f_idx = 0, pg = 0;                            // page ids of the warp's next 32 units of the sequence, one per lane
+  int f_n = 0, f_left = n_my;                       // stages used so far, units still to be fetched
+  const uint8_t* f_k = p.kd + (long long)f_h * p.dsh;
+  const uint8_t* f_v = p.vd + (long long)f_h * p.dsh;
+  const uint8_t* f_ks = p.ksf + (long long)f_h * p.ssh;
+  const uint8_t* f_vs = p.vsf + (long long)f_h * p.ssh;
+  const int* f_bt = p.bt + (long long)f_b * p.MP;
+  const int lps = 31 - __clz(p.PS);                 // page size is a power of two
 
-  auto issue_fetch = [&](int fi) {
-    const long long pos = lo + w + (long long)fi * TG;
-    seek(fw, pos);
-    const int nvalid = min(16, fw.r.L - 16 * fw.blk);
-    if (nvalid <= 0) return;                        // empty context: nothing to read
-    // page ids of this warp's next 32 units of the same sequence, one per lane
-    const int rel = (fw.blk - pg_blk0) / TG;
-    if (pg_b != fw.b || pg_h != fw.h || (fw.blk - pg_blk0) % TG != 0 || rel < 0 || rel >= 32) {
-      pg_b = fw.b; pg_h = fw.h; pg_blk0 = fw.blk;
-      const int blk_l = fw.blk + lane * TG;
-      pg = blk_l < fw.r.U ? __ldg(p.bt + (long long)fw.b * p.MP + (blk_l * 16) / p.PS) : 0;
+  auto fetch_slow = [&]() -> bool {                 // true: the unit carries no bytes and has been dealt with here
+    if (f_blk >= f_U) {                             // the cursor left its sequence: walk to the one that holds the unit
+      do {
+        f_blk -= f_U;
+        if (++f_h == KVH) {
+          f_h = 0;
+          ReqInfo r;
+          do { r = load_req(p, ++f_b); } while (r.U == 0);
+          f_U = r.U;
+          f_L = r.L;
+        }
+      } while (f_blk >= f_U);
+      f_k = p.kd + (long long)f_h * p.dsh;
+      f_v = p.vd + (long long)f_h * p.dsh;
+      f_ks = p.ksf + (long long)f_h * p.ssh;
+      f_vs = p.vsf + (long long)f_h * p.ssh;
+      f_bt = p.bt + (long long)f_b * p.MP;
     }
-    const int page = __shfl_sync(0xffffffffu, pg, (fw.blk - pg_blk0) / TG);
-    const int pos0 = (fw.blk * 16) % p.PS;
-    const int slot = fi % NS;
-    uint8_t* st = my_ring + slot * Gm::STAGE;
-    uint64_t* bar = my_bars + slot;
-    if (lane == 0) mbar_expect_tx(bar, Gm::STAGE);
-    __syncwarp();
-    const long long doff = (long long)page * p.dsp + (long long)pos0 * p.dst + (long long)fw.h * p.dsh;
-    if (LAYOUT == 0) {
-      if (lane == 0) bulk_g2s(st, p.kd + doff, Gm::TILE, bar);
-      if (lane == 1) bulk_g2s(st + Gm::TILE, p.vd + doff, Gm::TILE, bar);
-    } else {
-      const long long soff = (long long)page * p.ssp + (long long)pos0 * p.sst + (long long)fw.h * p.ssh;
-      if (lane == 0) bulk_g2s(st, p.kd + doff, 16 * Gm::SD, bar);
-      if (lane == 1) bulk_g2s(st + 16 * Gm::SD, p.ksf + soff, 16 * Gm::SS, bar);
-      if (lane == 2) bulk_g2s(st + Gm::TILE, p.vd + doff, 16 * Gm::SD, bar);
-      if (lane == 3) bulk_g2s(st + Gm::TILE + 16 * Gm::SD, p.vsf + soff, 16 * Gm::SS, bar);
+    if (f_L == 0) {                                 // an empty context has one unit and nothing to read: complete the
+      if (lane == 0) mbar_arrive(my_bars + f_n % NS);   // stage's phase with a plain arrival so that both sides stay in step
+      f_fast_end = 0;
+      return true;
     }
+    const int blk_l = f_blk + lane * TG;            // refill the page window from the current block
+    pg = blk_l < f_U ? __ldg(f_bt + ((blk_l * 16) >> lps)) : 0;
+    f_idx = 0;
+    f_fast_end = min(f_U, f_blk + 32 * TG);
+    return false;
+  };
+  auto fetch_one = [&]() {
+    bool empty = false;
+    if (f_blk >= f_fast_end) empty = fetch_slow();
+    if (!empty) {
+      const int page = __shfl_sync(0xffffffffu, pg, f_idx);
+      ++f_idx;
+      if (lane == 0) {
+        const int pos0 = (f_blk * 16) & (p.PS - 1);
+        const int slot = f_n % NS;
+        uint8_t* st = my_ring + slot * Gm::STAGE;
+        uint64_t* bar = my_bars + slot;
+        mbar_expect_tx(bar, Gm::STAGE);
+        const long long doff = (long long)page * p.dsp + (long long)pos0 * p.dst;
+        if (LAYOUT == 0) {
+          bulk_g2s(st, f_k + doff, Gm::TILE, bar);
+          bulk_g2s(st + Gm::TILE, f_v + doff, Gm::TILE, bar);
+        } else {
+          const long long soff = (long long)page * p.ssp + (long long)pos0 * p.sst;
+          bulk_g2s(st, f_k + doff, 16 * Gm::SD, bar);
+          bulk_g2s(st + 16 * Gm::SD, f_ks + soff, 16 * Gm::SS, bar);
+          bulk_g2s(st + Gm::TILE, f_v + doff, 16 * Gm::SD, bar);
+          bulk_g2s(st + Gm::TILE + 16 * Gm::SD, f_vs + soff, 16 * Gm::SS, bar);
+        }
+      }
+    }
+    f_blk += TG;
+    ++f_n;
+    --f_left;
   };
 
-  int fi = 0, ci = 0;
-  uint32_t phase_bits = 0;                          // bit s: parity the next wait on stage s must see
+  int c_n = 0;                                      // stages consumed so far
   bool dead = false;                                // a bounded wait ran out: stop consuming
-  for (; fi < min(NS, n_my); ++fi) issue_fetch(fi);
+  while (f_n < NS && f_left > 0) fetch_one();
+
+  // byte offsets of this lane's rows and blocks inside a stage (constant for the whole kernel)
+  const int r0 = Gm::tok(g), r1 = Gm::tok(g + 8);
+  const int t00 = Gm::tok(2 * c), t01 = Gm::tok(2 * c + 1), t10 = Gm::tok(2 * c + 8), t11 = Gm::tok(2 * c + 9);
+  const int koff_d = r0 * Gm::ROW + 8 * Gm::kblk(c, 0), koff_s = Gm::SF_BASE + r0 * Gm::SF_ROW + Gm::kblk(c, 0);
+  const int voff_d = Gm::TILE + t00 * Gm::ROW + 8 * g, voff_s = Gm::TILE + Gm::SF_BASE + t00 * Gm::SF_ROW + g;
+  constexpr int KR1 = (D == 128 && LAYOUT == 0) ? 1 : 8;                  // r1 - r0
+  constexpr int VR01 = (D == 128 && LAYOUT == 0) ? 2 : 1, VR10 = (D == 128 && LAYOUT == 0) ? 1 : 8,
+                VR11 = (D == 128 && LAYOUT == 0) ? 3 : 9;                 // t01 - t00, t10 - t00, t11 - t00
 
   // ---- compute side: walk the pieces of the partition
   long long pos = lo;
@@ -287,14 +334,20 @@ __global__ void __launch_bounds__(NTHREADS) decode_kernel(const DecodeParams p) 
       descs[part] = d;
     }
 
-    // this warp's units of the piece: local indices k = k_first, k_first + TG, .. < k0 + n_piece
-    const int k_first = k0 + ((w - k0) % TG + TG) % TG;
-    float m_run = NEG_BIG, l_run = 0.0f;
+    // this warp's blocks of the piece: blk_first, blk_first + TG, .. < blk_end
+    const int blk_first = blk0 + ((w - k0) % TG + TG) % TG, blk_end = blk0 + n_piece;
+    // running max (raw score units) and sum of query rows 2c and 2c+1 over this lane's tokens
+    float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;
     float o[Gm::KS][4];
 #pragma unroll
     for (int j = 0; j < Gm::KS; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
 
-    if (k_first < k0 + n_piece && !dead) {
+    if (blk_first < blk_end && !dead) {
+      // softmax scale in the log2 domain. A negative scale is moved into the query so that "max" stays a max.
+      float sc = p.scale_log2 * __ldg(p.gk + h);
+      const bool flip = sc < 0.0f;
+      sc = fmaxf(fabsf(sc), 1e-30f);
+      const float tau_raw = TAU / sc;
       // query fragments: row g of the (request, kv head) group, channels of this lane's key blocks, as f16
       uint32_t qa[Gm::KS][2];
       {
@@ -315,152 +368,157 @@ __global__ void __launch_bounds__(NTHREADS) decode_kernel(const DecodeParams p) 
             float a = __uint_as_float(ws[i] << 16), bq = __uint_as_float(ws[i] & 0xffff0000u);
             a = fminf(fmaxf(a, -65504.0f), 65504.0f);
             bq = fminf(fmaxf(bq, -65504.0f), 65504.0f);
+            if (flip) { a = -a; bq = -bq; }
             qa[4 * u + (i >> 1)][i & 1] = pack_f16x2(a, bq);
           }
         }
       }
-      const float sc = p.scale_log2 * __ldg(p.gk + h);
-      // visible context of this lane's query row (causal among the request's own query tokens)
-      const int lim = g < R ? L - ql + g / G + 1 : L;
-      const int lim_min = L - ql + 1;
+      // visible context of query rows 2c, 2c+1 (causal among the request's own query tokens)
+      const int lim0 = 2 * c < R ? L - ql + (2 * c) / G + 1 : L, lim1 = 2 * c + 1 < R ? L - ql + (2 * c + 1) / G + 1 : L;
+      const int blk_mask = (L - ql + 1) >> 4;        // blocks below this one are visible to every query row in full
+      float mneg0 = -m0 * sc, mneg1 = -m1 * sc;      // p = 2^(s * sc + mneg)
+      float thr0 = m0 + tau_raw, thr1 = m1 + tau_raw;
 
-      for (int k = k_first; k < k0 + n_piece; k += TG) {
-        const int blk = blk0 + (k - k0);
-        const int tbase = blk * 16;
-        const int nvalid = min(16, L - tbase);
-        if (nvalid > 0) {
-          const int slot = ci % NS;
-          if (!mbar_wait_bounded(my_bars + slot, (phase_bits >> slot) & 1u)) {
+      for (int blk = blk_first; blk < blk_end; blk += TG) {
+        const int slot = c_n % NS;
+        if (!mbar_try_wait(my_bars + slot, (c_n / NS) & 1)) {
+          if (!mbar_wait_bounded(my_bars + slot, (c_n / NS) & 1)) {
             if (lane == 0) atomicExch(&hdr->status, HKV_ERR_DEVICE_WAIT);
             dead = true;
             break;
           }
-          phase_bits ^= 1u << slot;
-          const uint8_t* kt = my_ring + slot * Gm::STAGE;
-          const uint8_t* vt = kt + Gm::TILE;
+        }
+        ++c_n;
+        if (L > 0) {                                  // (the single unit of an empty context carries nothing)
+          const uint8_t* st = my_ring + slot * Gm::STAGE;
+          const uint8_t* kd_ = st + koff_d;
+          const uint8_t* ks_ = st + koff_s;
+          const uint8_t* vd_ = st + voff_d;
+          const uint8_t* vs_ = st + voff_s;
+          const bool masked = blk >= blk_mask;        // warp-uniform: only the last block(s) of a sequence
 
-          // ---------------- S = Q K^T : two score tiles of 8 tokens each, rows = query rows
-          float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-          const int r0 = Gm::tok(0, g), r1 = Gm::tok(1, g);
+          // ---------------- S^T = K Q^T : rows = the 16 tokens, columns = query rows; two accumulators so that
+          // consecutive mma do not wait for each other
+          float sa0[4] = {0.f, 0.f, 0.f, 0.f}, sa1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int u = 0; u < Gm::NBL; ++u) {
-            const int kb = Gm::kblk(c, u);
-            const uint2 w0 = *reinterpret_cast<const uint2*>(kt + r0 * Gm::ROW + 8 * kb);
-            const uint2 w1 = *reinterpret_cast<const uint2*>(kt + r1 * Gm::ROW + 8 * kb);
-            const uint32_t f0 = kt[Gm::SF_BASE + r0 * Gm::SF_ROW + kb], f1 = kt[Gm::SF_BASE + r1 * Gm::SF_ROW + kb];
-            const uint32_t sf0 = e4m3x2_to_f16x2(f0 | (f0 << 8)), sf1 = e4m3x2_to_f16x2(f1 | (f1 << 8));
+            constexpr int dummy = 0;
+            (void)dummy;
+            const int du = 8 * (Gm::kblk(0, u) - Gm::kblk(0, 0)), su = Gm::kblk(0, u) - Gm::kblk(0, 0);
+            const uint2 w0 = *reinterpret_cast<const uint2*>(kd_ + du);
+            const uint2 w1 = *reinterpret_cast<const uint2*>(kd_ + du + KR1 * Gm::ROW);
+            const uint32_t f0 = ks_[su], f1 = ks_[su + KR1 * Gm::SF_ROW];
+            const __half2 sf = u32_as_h2(e4m3x2_to_f16x2(f0 | (f1 << 8)));     // (scale of row r0, scale of row r1)
+            const __half2 sf0 = __low2half2(sf), sf1 = __high2half2(sf);
             uint32_t e0[4], e1[4], e2[4], e3[4];
             e2m1x8_to_f16x2(w0.x, e0);
             e2m1x8_to_f16x2(w0.y, e1);
             e2m1x8_to_f16x2(w1.x, e2);
             e2m1x8_to_f16x2(w1.y, e3);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              e0[i] = hmul2(e0[i], sf0);
-              e1[i] = hmul2(e1[i], sf0);
-              e2[i] = hmul2(e2[i], sf1);
-              e3[i] = hmul2(e3[i], sf1);
-            }
-            mma_f16(s0, qa[4 * u + 0][0], 0u, qa[4 * u + 0][1], 0u, e0[0], e0[1]);
-            mma_f16(s0, qa[4 * u + 1][0], 0u, qa[4 * u + 1][1], 0u, e0[2], e0[3]);
-            mma_f16(s0, qa[4 * u + 2][0], 0u, qa[4 * u + 2][1], 0u, e1[0], e1[1]);
-            mma_f16(s0, qa[4 * u + 3][0], 0u, qa[4 * u + 3][1], 0u, e1[2], e1[3]);
-            mma_f16(s1, qa[4 * u + 0][0], 0u, qa[4 * u + 0][1], 0u, e2[0], e2[1]);
-            mma_f16(s1, qa[4 * u + 1][0], 0u, qa[4 * u + 1][1], 0u, e2[2], e2[3]);
-            mma_f16(s1, qa[4 * u + 2][0], 0u, qa[4 * u + 2][1], 0u, e3[0], e3[1]);
-            mma_f16(s1, qa[4 * u + 3][0], 0u, qa[4 * u + 3][1], 0u, e3[2], e3[3]);
+            // k-step v of this block: A = {row r0 k-low, row r1 k-low, row r0 k-high, row r1 k-high}
+            mma_f16(sa0, hmul2h(e0[0], sf0), hmul2h(e2[0], sf1), hmul2h(e0[1], sf0), hmul2h(e2[1], sf1), qa[4 * u + 0][0],
+                    qa[4 * u + 0][1]);
+            mma_f16(sa1, hmul2h(e0[2], sf0), hmul2h(e2[2], sf1), hmul2h(e0[3], sf0), hmul2h(e2[3], sf1), qa[4 * u + 1][0],
+                    qa[4 * u + 1][1]);
+            mma_f16(sa0, hmul2h(e1[0], sf0), hmul2h(e3[0], sf1), hmul2h(e1[1], sf0), hmul2h(e3[1], sf1), qa[4 * u + 2][0],
+                    qa[4 * u + 2][1]);
+            mma_f16(sa1, hmul2h(e1[2], sf0), hmul2h(e3[2], sf1), hmul2h(e1[3], sf0), hmul2h(e3[3], sf1), qa[4 * u + 3][0],
+                    qa[4 * u + 3][1]);
           }
 
-          // ---------------- online softmax for query row g over this lane's 4 tokens
-          const int t00 = Gm::tok(0, 2 * c), t01 = Gm::tok(0, 2 * c + 1), t10 = Gm::tok(1, 2 * c),
-                    t11 = Gm::tok(1, 2 * c + 1);
-          float x0 = s0[0] * sc, x1 = s0[1] * sc, x2 = s1[0] * sc, x3 = s1[1] * sc;
-          if (tbase + 16 > lim_min) {                 // warp-uniform: only the last block(s) of a sequence
+          // ---------------- online softmax (raw score units): this lane holds query rows 2c, 2c+1 of tokens r0, r1
+          float x00 = sa0[0] + sa1[0], x01 = sa0[1] + sa1[1], x10 = sa0[2] + sa1[2], x11 = sa0[3] + sa1[3];
+          if (masked) {
             const float ninf = -__int_as_float(0x7f800000);
-            x0 = tbase + t00 < lim ? x0 : ninf;
-            x1 = tbase + t01 < lim ? x1 : ninf;
-            x2 = tbase + t10 < lim ? x2 : ninf;
-            x3 = tbase + t11 < lim ? x3 : ninf;
+            const int tbase = blk * 16;
+            x00 = tbase + r0 < lim0 ? x00 : ninf;
+            x01 = tbase + r0 < lim1 ? x01 : ninf;
+            x10 = tbase + r1 < lim0 ? x10 : ninf;
+            x11 = tbase + r1 < lim1 ? x11 : ninf;
           }
-          float bm = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
-          bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
-          bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
-          bm = fmaxf(bm, NEG_BIG);
-          if (__any_sync(0xffffffffu, bm > m_run + TAU)) {
-            const float m_new = fmaxf(m_run, bm);
-            const float alpha = fast_exp2(m_run - m_new);
-            m_run = m_new;
-            l_run *= alpha;
-            const float a0 = __shfl_sync(0xffffffffu, alpha, 8 * c), a1 = __shfl_sync(0xffffffffu, alpha, 8 * c + 4);
+          // the running max moves only when some score exceeds it by more than TAU (then P stays below 2^TAU, inside
+          // f16); the cross-lane maximum is needed only in that case
+          float bm0 = fmaxf(x00, x10), bm1 = fmaxf(x01, x11);
+          if (__any_sync(0xffffffffu, (bm0 > thr0) | (bm1 > thr1))) {
+#pragma unroll
+            for (int of = 4; of < 32; of <<= 1) {
+              bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, of));
+              bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, of));
+            }
+            const float n0 = fmaxf(m0, fmaxf(bm0, NEG_BIG)), n1 = fmaxf(m1, fmaxf(bm1, NEG_BIG));
+            const float al0 = fast_exp2((m0 - n0) * sc), al1 = fast_exp2((m1 - n1) * sc);
+            m0 = n0; m1 = n1;
+            mneg0 = -n0 * sc; mneg1 = -n1 * sc;
+            thr0 = n0 + tau_raw; thr1 = n1 + tau_raw;
+            l0 *= al0; l1 *= al1;
 #pragma unroll
             for (int j = 0; j < Gm::KS; ++j) {
-              o[j][0] *= a0; o[j][1] *= a1; o[j][2] *= a0; o[j][3] *= a1;
+              o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1;
             }
           }
-          const float p0 = fast_exp2(x0 - m_run), p1 = fast_exp2(x1 - m_run), p2 = fast_exp2(x2 - m_run),
-                      p3 = fast_exp2(x3 - m_run);
-          l_run += (p0 + p1) + (p2 + p3);
-          const uint32_t pb0 = pack_f16x2(p0, p1), pb1 = pack_f16x2(p2, p3);
+          const float p00 = fast_exp2(fmaf(x00, sc, mneg0)), p01 = fast_exp2(fmaf(x01, sc, mneg1)),
+                      p10 = fast_exp2(fmaf(x10, sc, mneg0)), p11 = fast_exp2(fmaf(x11, sc, mneg1));
+          l0 += p00 + p10;
+          l1 += p01 + p11;
+          // P^T as the B operand of the second product: transpose the two 8x8 (token, row) tiles
+          const uint32_t pb0 = movmatrix_trans(pack_f16x2(p00, p01)), pb1 = movmatrix_trans(pack_f16x2(p10, p11));
 
           // ---------------- O^T += V^T P^T : rows = channels of block g (+8), columns = query rows
-          const bool tail = nvalid < 16;
 #pragma unroll
           for (int hf = 0; hf < Gm::NH; ++hf) {
-            const int vb = g + 8 * hf;
-            const uint2 v00 = *reinterpret_cast<const uint2*>(vt + t00 * Gm::ROW + 8 * vb);
-            const uint2 v01 = *reinterpret_cast<const uint2*>(vt + t01 * Gm::ROW + 8 * vb);
-            const uint2 v10 = *reinterpret_cast<const uint2*>(vt + t10 * Gm::ROW + 8 * vb);
-            const uint2 v11 = *reinterpret_cast<const uint2*>(vt + t11 * Gm::ROW + 8 * vb);
-            uint32_t f00 = vt[Gm::SF_BASE + t00 * Gm::SF_ROW + vb], f01 = vt[Gm::SF_BASE + t01 * Gm::SF_ROW + vb];
-            uint32_t f10 = vt[Gm::SF_BASE + t10 * Gm::SF_ROW + vb], f11 = vt[Gm::SF_BASE + t11 * Gm::SF_ROW + vb];
-            if (tail) {                               // rows past the context hold arbitrary bytes: read them as 0
+            const uint2 v00 = *reinterpret_cast<const uint2*>(vd_ + 64 * hf);
+            const uint2 v01 = *reinterpret_cast<const uint2*>(vd_ + 64 * hf + VR01 * Gm::ROW);
+            const uint2 v10 = *reinterpret_cast<const uint2*>(vd_ + 64 * hf + VR10 * Gm::ROW);
+            const uint2 v11 = *reinterpret_cast<const uint2*>(vd_ + 64 * hf + VR11 * Gm::ROW);
+            uint32_t f00 = vs_[8 * hf], f01 = vs_[8 * hf + VR01 * Gm::SF_ROW];
+            uint32_t f10 = vs_[8 * hf + VR10 * Gm::SF_ROW], f11 = vs_[8 * hf + VR11 * Gm::SF_ROW];
+            if (masked) {                             // rows past the context hold arbitrary bytes: read them as 0
+              const int nvalid = L - blk * 16;
               f00 = t00 < nvalid ? f00 : 0u;
               f01 = t01 < nvalid ? f01 : 0u;
               f10 = t10 < nvalid ? f10 : 0u;
               f11 = t11 < nvalid ? f11 : 0u;
             }
-            const uint32_t sa = e4m3x2_to_f16x2(f00 | (f01 << 8)), sb = e4m3x2_to_f16x2(f10 | (f11 << 8));
-            // bytes of (token pair, channel): low nibble = first token of the pair, high nibble = second
+            const __half2 sa = u32_as_h2(e4m3x2_to_f16x2(f00 | (f01 << 8))), sb = u32_as_h2(e4m3x2_to_f16x2(f10 | (f11 << 8)));
             const uint32_t M = 0x0f0f0f0fu;
-            const uint32_t xe0 = (v00.x & M) | ((v01.x & M) << 4), xo0 = ((v00.x >> 4) & M) | (v01.x & ~M);
-            const uint32_t xe1 = (v00.y & M) | ((v01.y & M) << 4), xo1 = ((v00.y >> 4) & M) | (v01.y & ~M);
-            const uint32_t ye0 = (v10.x & M) | ((v11.x & M) << 4), yo0 = ((v10.x >> 4) & M) | (v11.x & ~M);
-            const uint32_t ye1 = (v10.y & M) | ((v11.y & M) << 4), yo1 = ((v10.y >> 4) & M) | (v11.y & ~M);
-            uint32_t ae[8], ao[8], be[8], bo[8];      // [channel pair jj] -> f16x2 over (first, second) token
-            {
-              uint32_t t4[4];
-              e2m1x8_to_f16x2(xe0, t4); ae[0] = t4[0]; ae[1] = t4[1]; ae[2] = t4[2]; ae[3] = t4[3];
-              e2m1x8_to_f16x2(xe1, t4); ae[4] = t4[0]; ae[5] = t4[1]; ae[6] = t4[2]; ae[7] = t4[3];
-              e2m1x8_to_f16x2(xo0, t4); ao[0] = t4[0]; ao[1] = t4[1]; ao[2] = t4[2]; ao[3] = t4[3];
-              e2m1x8_to_f16x2(xo1, t4); ao[4] = t4[0]; ao[5] = t4[1]; ao[6] = t4[2]; ao[7] = t4[3];
-              e2m1x8_to_f16x2(ye0, t4); be[0] = t4[0]; be[1] = t4[1]; be[2] = t4[2]; be[3] = t4[3];
-              e2m1x8_to_f16x2(ye1, t4); be[4] = t4[0]; be[5] = t4[1]; be[6] = t4[2]; be[7] = t4[3];
-              e2m1x8_to_f16x2(yo0, t4); bo[0] = t4[0]; bo[1] = t4[1]; bo[2] = t4[2]; bo[3] = t4[3];
-              e2m1x8_to_f16x2(yo1, t4); bo[4] = t4[0]; bo[5] = t4[1]; bo[6] = t4[2]; bo[7] = t4[3];
-            }
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj)
-              mma_f16(o[8 * hf + jj], hmul2(ae[jj], sa), hmul2(ao[jj], sa), hmul2(be[jj], sb), hmul2(bo[jj], sb), pb0,
-                      pb1);
+            for (int wv = 0; wv < 2; ++wv) {
+              const uint32_t a0 = wv ? v00.y : v00.x, a1 = wv ? v01.y : v01.x, b0_ = wv ? v10.y : v10.x,
+                             b1_ = wv ? v11.y : v11.x;
+              // bytes of (token pair, channel): low nibble = first token of the pair, high nibble = second
+              const uint32_t xe = (a0 & M) | ((a1 * 16u) & ~M), xo = ((a0 >> 4) & M) | (a1 & ~M);
+              const uint32_t ye = (b0_ & M) | ((b1_ * 16u) & ~M), yo = ((b0_ >> 4) & M) | (b1_ & ~M);
+              uint32_t ae[4], ao[4], be[4], bo[4];   // [channel pair] -> f16x2 over (first, second) token
+              e2m1x8_to_f16x2(xe, ae);
+              e2m1x8_to_f16x2(xo, ao);
+              e2m1x8_to_f16x2(ye, be);
+              e2m1x8_to_f16x2(yo, bo);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                mma_f16(o[8 * hf + 4 * wv + i], hmul2h(ae[i], sa), hmul2h(ao[i], sa), hmul2h(be[i], sb), hmul2h(bo[i], sb),
+                        pb0, pb1);
+            }
           }
           __syncwarp();
         }
-        ++ci;
-        if (fi < n_my) {
-          issue_fetch(fi);
-          ++fi;
-        }
+        if (f_left > 0) fetch_one();
       }
     }
 
     // ---------------- merge the TG warps' states of this piece and write it out
     {
-      float l_tot = l_run;
-      l_tot += __shfl_xor_sync(0xffffffffu, l_tot, 1);
-      l_tot += __shfl_xor_sync(0xffffffffu, l_tot, 2);
-      if (c == 0) {
-        mbuf[w * RPAD + g] = m_run;
-        lbuf[w * RPAD + g] = l_tot;
+#pragma unroll
+      for (int of = 4; of < 32; of <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, of);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, of);
+      }
+      float sc = p.scale_log2 * __ldg(p.gk + h);
+      sc = fmaxf(fabsf(sc), 1e-30f);
+      if (g == 0) {
+        mbuf[w * RPAD + 2 * c] = m0 * sc;          // log2 units from here on
+        mbuf[w * RPAD + 2 * c + 1] = m1 * sc;
+        lbuf[w * RPAD + 2 * c] = l0;
+        lbuf[w * RPAD + 2 * c + 1] = l1;
       }
       float* ob = obuf + (size_t)w * RPAD * Sm::OROW;
 #pragma unroll
@@ -477,7 +535,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_kernel(const DecodeParams p) 
       const int slot_id = part * 2 + (piece_idx == 0 ? 0 : 1);
       for (int idx = tid; idx < R * (D / 2); idx += NTHREADS) {
         const int row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
-        float mx = NEG_BIG;
+        float mx = -3.0e38f;
 #pragma unroll
         for (int ww = 0; ww < TG; ++ww) mx = fmaxf(mx, mbuf[ww * RPAD + row]);
         float den = 0.0f, n0 = 0.0f, n1 = 0.0f;
@@ -508,7 +566,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_kernel(const DecodeParams p) 
   // a warp that gave up may still have copies in flight: wait for them (bounded) before the CTA's shared memory is
   // released
   if (dead) {
-    for (int i = 0; i < NS; ++i) (void)mbar_wait_bounded(my_bars + i, (phase_bits >> i) & 1u);
+    for (int i = c_n; i < f_n; ++i) (void)mbar_wait_bounded(my_bars + i % NS, (i / NS) & 1);
   }
 }
 
@@ -569,7 +627,7 @@ static DeviceInfo g_dev[64];
 
 template <int D, int LAYOUT>
 struct Pick {
-  static constexpr int NS = D == 128 ? 4 : 3;
+  static constexpr int NS = 4;                       // stages per warp (a power of two keeps the slot arithmetic cheap)
 };
 
 template <int D, int LAYOUT>
@@ -629,7 +687,7 @@ extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const 
     return HKV_ERR_NULL;
   if (D != 128 && D != 256) return HKV_ERR_UNSUPPORTED;
   if (KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > RPAD) return HKV_ERR_UNSUPPORTED;
-  if (PS < 16 || PS % 16 != 0) return HKV_ERR_UNSUPPORTED;
+  if (PS < 16 || (PS & (PS - 1)) != 0) return HKV_ERR_UNSUPPORTED;   // 16, 32, 64, ..
   if (B > kMaxBatch) return HKV_ERR_RANGE;
   if (splits < 0) return HKV_ERR_RANGE;
   if (splits > 64) return HKV_ERR_SPLITS;

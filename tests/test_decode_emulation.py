@@ -53,11 +53,22 @@ class Geo:
         self.SF_ROW = self.SLOT if layout == 0 else self.SS
         self.KS, self.NBL, self.NH = D // 16, D // 64, D // 128
 
-    def tok(self, t, n):
-        return 2 * n + t if (self.D == 128 and self.layout == 0) else n + 8 * t
+    def tok(self, i):
+        return 2 * (i & 7) + (i >> 3) if (self.D == 128 and self.layout == 0) else i
 
     def kblk(self, c, u):
         return c + 4 * u if self.D == 128 else 2 * c + (u & 1) + 8 * (u >> 1)
+
+
+def movmatrix_trans(regs):
+    """movmatrix.sync.aligned.m8n8.trans.b16: lane l holds row l // 4, columns 2 (l % 4), 2 (l % 4) + 1"""
+    m = np.zeros((8, 8))
+    for lane in range(32):
+        m[lane >> 2, 2 * (lane & 3)], m[lane >> 2, 2 * (lane & 3) + 1] = regs[lane]
+    out = np.zeros_like(regs)
+    for lane in range(32):
+        out[lane] = m.T[lane >> 2, 2 * (lane & 3)], m.T[lane >> 2, 2 * (lane & 3) + 1]
+    return out
 
 
 def make_tile(seed, geo):
@@ -77,7 +88,7 @@ def emulate_unit(geo, kt, vt, q, wrong=None):
     the kernel's fragments would hold them."""
     D = geo.D
     sf_val = O.e4m3_decode(np.arange(256, dtype=np.uint8))
-    # query fragments qa[lane][kstep][2 regs][2 halves]
+    # query fragments qa[lane][kstep][2 regs][2 halves]: row g, channels of the lane's key blocks
     qa = np.zeros((32, geo.KS, 2, 2))
     for lane in range(32):
         g, c = lane >> 2, lane & 3
@@ -85,37 +96,29 @@ def emulate_unit(geo, kt, vt, q, wrong=None):
             ch0 = 16 * geo.kblk(c, u)
             for i in range(8):
                 qa[lane, 4 * u + (i >> 1), i & 1] = q[g, ch0 + 2 * i], q[g, ch0 + 2 * i + 1]
-    s = [np.zeros((32, 4)), np.zeros((32, 4))]
+    st = np.zeros((32, 4))                             # S^T tile: rows = tokens, columns = query rows
     for u in range(geo.NBL):
-        e = np.zeros((2, 32, 8, 2))                  # [tile][lane][byte of the block][half]
+        e = np.zeros((2, 32, 8, 2))                  # [token of the lane][lane][byte of the block][half]
         for lane in range(32):
             g, c = lane >> 2, lane & 3
             kb = geo.kblk(c, u)
             if wrong == "kblock" and u == 0:
                 kb = geo.kblk((c + 1) % 4, u)
             for t in range(2):
-                r = geo.tok(t, g)
+                r = geo.tok(g + 8 * t)
                 scale = sf_val[kt[geo.SF_BASE + r * geo.SF_ROW + kb]]
                 for by in range(8):
                     lo, hi = cvt_byte(int(kt[r * geo.ROW + 8 * kb + by]))
                     e[t, lane, by] = lo * scale, hi * scale
         for v in range(4):
-            a = np.zeros((32, 4, 2))
-            a[:, 0] = qa[:, 4 * u + v, 0]
-            a[:, 2] = qa[:, 4 * u + v, 1]
-            for t in range(2):
-                b = np.stack([e[t, :, 2 * v], e[t, :, 2 * v + 1]], axis=1)
-                s[t] = mma_m16n8k16(a, b, s[t])
+            a = np.stack([e[0, :, 2 * v], e[1, :, 2 * v], e[0, :, 2 * v + 1], e[1, :, 2 * v + 1]], axis=1)
+            st = mma_m16n8k16(a, qa[:, 4 * u + v], st)
     S = np.zeros((8, 16))
-    pb = np.zeros((32, 2, 2))
     for lane in range(32):
         g, c = lane >> 2, lane & 3
-        toks = (geo.tok(0, 2 * c), geo.tok(0, 2 * c + 1), geo.tok(1, 2 * c), geo.tok(1, 2 * c + 1))
-        vals = (s[0][lane, 0], s[0][lane, 1], s[1][lane, 0], s[1][lane, 1])
-        for tk, x in zip(toks, vals):
-            S[g, tk] = x
-        pb[lane, 0] = vals[0], vals[1]
-        pb[lane, 1] = vals[2], vals[3]
+        S[2 * c, geo.tok(g)], S[2 * c + 1, geo.tok(g)] = st[lane, 0], st[lane, 1]
+        S[2 * c, geo.tok(g + 8)], S[2 * c + 1, geo.tok(g + 8)] = st[lane, 2], st[lane, 3]
+    pb = np.stack([movmatrix_trans(st[:, 0:2]), movmatrix_trans(st[:, 2:4])], axis=1)
     o = np.zeros((geo.KS, 32, 4))
     for hf in range(geo.NH):
         for jj in range(8):
@@ -123,7 +126,7 @@ def emulate_unit(geo, kt, vt, q, wrong=None):
             for lane in range(32):
                 g, c = lane >> 2, lane & 3
                 vb = g + 8 * hf
-                toks = [geo.tok(0, 2 * c), geo.tok(0, 2 * c + 1), geo.tok(1, 2 * c), geo.tok(1, 2 * c + 1)]
+                toks = [geo.tok(2 * c), geo.tok(2 * c + 1), geo.tok(2 * c + 8), geo.tok(2 * c + 9)]
                 if wrong == "vtokens":
                     toks[0], toks[1] = toks[1], toks[0]
                 w = [vt[t * geo.ROW + 8 * vb:t * geo.ROW + 8 * vb + 8].astype(np.int64) for t in toks]
@@ -184,7 +187,7 @@ def test_value_loads_hit_distinct_banks():
                 banks = []
                 for lane in range(16 * half, 16 * half + 16):
                     g, c = lane >> 2, lane & 3
-                    t = (geo.tok(0, 2 * c), geo.tok(0, 2 * c + 1), geo.tok(1, 2 * c), geo.tok(1, 2 * c + 1))[which]
+                    t = (geo.tok(2 * c), geo.tok(2 * c + 1), geo.tok(2 * c + 8), geo.tok(2 * c + 9))[which]
                     addr = t * geo.ROW + 8 * g
                     banks += [(addr // 4) % 32, (addr // 4 + 1) % 32]
                 assert len(set(banks)) == 32, (D, which, half)
