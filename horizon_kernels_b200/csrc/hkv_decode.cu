@@ -1,21 +1,22 @@
 // Paged split-K flash-decoding over the NVFP4 KV cache, and the log-sum-exp combine (sm_100a).
 //
-// Work decomposition ("balanced split-K"): the unit of work is one 16-token block of one (request, kv head)
-// sequence. All units of a batch, ordered (request, kv head, block), form one stream that is cut into equal
-// partitions, one per CTA of a grid that fills the GPU exactly once. A CTA therefore streams the same number of
-// cache bytes as every other CTA whatever the mix of context lengths. Inside a partition, a run of units of the same
-// (request, kv head) is a *piece*. A piece that covers its whole sequence is finished by the CTA and written to the
-// output; other pieces leave a normalised fp32 partial and a log2-sum-exp in the workspace, which the combine kernel
-// merges in partition order (fixed order => deterministic results).
+// Work decomposition ("balanced split-K"): the unit of work is UT consecutive tokens (32 at head_dim 128, 16 at 256)
+// of one (request, kv head) sequence. All units of a batch, ordered (request, kv head, position), form one stream that
+// is cut into equal partitions, one per CTA of a grid that fills the GPU exactly once. A CTA therefore streams the same
+// number of cache bytes as every other CTA whatever the mix of context lengths. Inside a partition, a run of units of
+// the same (request, kv head) is a *piece*. A piece that covers its whole sequence is finished by the CTA and written
+// to the output; other pieces leave a normalised fp32 partial and a log2-sum-exp in the workspace, which the combine
+// kernel merges in partition order (fixed order => deterministic results).
 //
 // Inside a CTA, TG warps take the partition's units round-robin. Every warp owns a private ring of NS shared-memory
 // stages; it issues 1-D bulk copies (cp.async.bulk, completion on an mbarrier) for its own future units, driven by
-// the block table, and consumes them in order, so the main loop needs no cross-warp synchronisation. Per unit a warp
-// computes S = Q K^T with mma.m16n8k16 (A = query rows padded to 16, B = 16 keys dequantised in registers from E2M1
-// codes with cvt.rn.f16x2.e2m1x2 and one f16x2 multiply by the E4M3 block scale), a warp-shuffle online softmax in the
-// log2 domain, and O^T += V^T P^T with A = dequantised values. code * scale is exact in f16 (at most 5 significant
-// bits, magnitude in [2^-10, 2688]), so the only roundings are P to f16 and the fp32 accumulations.
-// At the end of a piece the TG warps merge their (max, sum, accumulator) states through shared memory.
+// the block table, and consumes them in order, so the main loop needs no cross-warp synchronisation. Per 16 tokens a
+// warp computes S^T = K Q^T with mma.m16n8k16 (A = 16 keys dequantised in registers from E2M1 codes with
+// cvt.rn.f16x2.e2m1x2 and one f16x2 multiply by the E4M3 block scale, B = the query rows), an online softmax in the
+// log2 domain whose running maximum moves lazily, a movmatrix transpose of P, and O^T += V^T P^T with A = dequantised
+// values. code * scale is exact in f16 (at most 5 significant bits, magnitude in [2^-10, 2688]), so the only roundings
+// are P to f16 and the fp32 accumulations. At the end of a piece the TG warps merge their (max, sum, accumulator)
+// states through shared memory.
 //
 // Every wait on an mbarrier is bounded (hkv::kWaitCycles); when one runs out the kernel records
 // HKV_ERR_DEVICE_WAIT in the workspace header, stops consuming and returns.
@@ -52,33 +53,39 @@ struct DecodeParams {
   float scale_log2, v_scale;
 };
 
-// Shared-memory geometry of one stage (K tile then V tile of 16 tokens) for head_dim D and cache layout LAYOUT:
+// Shared-memory geometry of one stage (K tile then V tile of one unit) for head_dim D and cache layout LAYOUT:
 //   LAYOUT 0  token rows of [D/2 code bytes | D/16 scale bytes] back to back (the serving "slot" layout with heads
-//             outermost inside a page): one bulk copy of 16 * slot bytes per tile
-//   LAYOUT 1  16 code rows back to back, then 16 scale rows (the page-region layout of the reference's torch oracle):
-//             two bulk copies per tile
+//             outermost inside a page): one bulk copy of 16 * slot bytes per 16 tokens and side
+//   LAYOUT 1  code rows back to back, then the scale rows (the page-region layout of the reference's torch oracle):
+//             two bulk copies per 16 tokens and side
 template <int D, int LAYOUT>
 struct Geo {
   static constexpr int SD = D / 2, SS = D / 16, SLOT = SD + SS;
-  static constexpr int TILE = 16 * SLOT;               // bytes of one (head, side) tile of 16 tokens
+  static constexpr int UB = D == 128 ? 2 : 1;          // 16-token blocks per unit
+  static constexpr int UT = 16 * UB, LOG_UT = UB == 2 ? 5 : 4;
+  static constexpr int NS = D == 128 ? 3 : 4;          // stages per warp
+  static constexpr int MINB = D == 128 ? 3 : 2;        // CTAs per SM the register budget is sized for
+  static constexpr int TILE = UT * SLOT;               // bytes of one (head, side) tile of a unit
   static constexpr int STAGE = 2 * TILE;
   static constexpr int ROW = LAYOUT == 0 ? SLOT : SD;  // byte stride between code rows in shared memory
-  static constexpr int SF_BASE = LAYOUT == 0 ? SD : 16 * SD;
+  static constexpr int SF_BASE = LAYOUT == 0 ? SD : UT * SD;
   static constexpr int SF_ROW = LAYOUT == 0 ? SLOT : SS;
-  static constexpr int KS = D / 16;                    // k-steps of Q K^T == mma tiles of P V
+  static constexpr int KS = D / 16;                    // k-steps of K Q^T == mma tiles of V^T P^T (per 16 tokens)
   static constexpr int NBL = D / 64;                   // 16-channel blocks of one key row held by one lane
   static constexpr int NH = D / 128;                   // 16-channel blocks of one value row held by one lane
-  // token (row of the stage) handled by row i of the 16-row score tile (chosen so that the value loads of a warp hit
-  // distinct shared-memory banks)
+  static constexpr int NCH = UB == 1 ? 2 : 1;          // independent accumulators per score tile
+  // token (row of a 16-token block) handled by row i of the 16-row score tile (chosen so that the value loads of a
+  // warp hit distinct shared-memory banks)
   __device__ static constexpr int tok(int i) { return (D == 128 && LAYOUT == 0) ? 2 * (i & 7) + (i >> 3) : i; }
   // 16-channel block of a key row held by lane column c as its u-th block
   __device__ static constexpr int kblk(int c, int u) { return D == 128 ? c + 4 * u : 2 * c + (u & 1) + 8 * (u >> 1); }
 };
 
-// walks the (request, kv head) sequences of the unit stream; all fields are warp-uniform
+// one request as the unit stream sees it; all fields are warp-uniform
 struct ReqInfo {
-  int U, L, ql, q0;
+  int U, L, ql, q0;                                    // units per kv head, context length, query tokens, first query row
 };
+template <int LOG_UT>
 __device__ __forceinline__ ReqInfo load_req(const DecodeParams& p, int b) {
   ReqInfo r;
   r.q0 = __ldg(p.qsl + b);
@@ -86,25 +93,26 @@ __device__ __forceinline__ ReqInfo load_req(const DecodeParams& p, int b) {
   ql = (ql < 0 || ql > p.qlmax) ? 0 : ql;
   r.ql = ql;
   r.L = ql > 0 ? max(__ldg(p.seq_lens + b), 0) : 0;
-  r.U = ql > 0 ? max(1, (r.L + 15) >> 4) : 0;
+  r.U = ql > 0 ? max(1, (r.L + (1 << LOG_UT) - 1) >> LOG_UT) : 0;
   return r;
 }
 
-template <int D, int LAYOUT, int NS>
+template <int D, int LAYOUT>
 struct Smem {
   using G_ = Geo<D, LAYOUT>;
-  static constexpr int RING = TG * NS * G_::STAGE;
-  static constexpr int BARS = TG * NS * 8;
+  static constexpr int RING = TG * G_::NS * G_::STAGE;
+  static constexpr int BARS = TG * G_::NS * 8;
   static constexpr int OROW = D + 4;                               // padded accumulator row (floats)
   static constexpr int MERGE = TG * RPAD * OROW * 4 + TG * RPAD * 2 * 4;
   static constexpr int COARSE = (kMaxBatch / 32 + 2) * 4;
   static constexpr int TOTAL = RING + BARS + MERGE + COARSE + 64;
 };
 
-template <int D, int LAYOUT, int NS>
-__global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(const DecodeParams p) {
+template <int D, int LAYOUT>
+__global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(const DecodeParams p) {
   using Gm = Geo<D, LAYOUT>;
-  using Sm = Smem<D, LAYOUT, NS>;
+  using Sm = Smem<D, LAYOUT>;
+  constexpr int NS = Gm::NS, UB = Gm::UB, UT = Gm::UT, LOG_UT = Gm::LOG_UT;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Sm::RING);
@@ -126,14 +134,14 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
   const int ngrp = (B + 31) >> 5;
   for (int grp = w; grp < ngrp; grp += TG) {
     const int b = grp * 32 + lane;
-    int u = b < B ? load_req(p, b).U : 0;
+    int u = b < B ? load_req<LOG_UT>(p, b).U : 0;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) u += __shfl_xor_sync(0xffffffffu, u, o);
     if (lane == 0) coarse[grp + 1] = u;
   }
   if (tid < TG * NS) mbar_init(bars + tid, 1);
   __syncthreads();
-  if (w == 0) {                                   // exclusive scan of up to kMaxBatch / 32 group sums
+  if (w == 0) {                                   // scan of up to kMaxBatch / 32 group sums
     const int per_lane = (ngrp + 31) >> 5;
     int s = 0;
     for (int i = 0; i < per_lane; ++i) {
@@ -184,7 +192,7 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
       if ((long long)coarse[mid] * KVH <= lo) lo_g = mid; else hi_g = mid;
     }
     const int b = lo_g * 32 + lane;
-    const int u = b < B ? load_req(p, b).U : 0;
+    const int u = b < B ? load_req<LOG_UT>(p, b).U : 0;
     int incl = u;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -200,7 +208,7 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
   // ---- compute-side walker over the pieces of the partition (identical in every warp)
   struct Walker {
     int b, h, blk;
-    long long seq0;                                // stream position of block 0 of (b, h)
+    long long seq0;                                // stream position of unit 0 of (b, h)
     ReqInfo r;
   };
   auto seek = [&](Walker& wk, long long pos) {     // move to the sequence that holds pos (pos < total)
@@ -210,29 +218,41 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
       wk.seq0 = end_h;
       if (++wk.h == KVH) {
         wk.h = 0;
-        do { wk.r = load_req(p, ++wk.b); } while (wk.r.U == 0);
+        do { wk.r = load_req<LOG_UT>(p, ++wk.b); } while (wk.r.U == 0);
       }
     }
     wk.blk = (int)(pos - wk.seq0);
   };
   Walker cw;
   cw.b = b0;
-  cw.r = load_req(p, b0);
+  cw.r = load_req<LOG_UT>(p, b0);
   cw.h = (int)((lo - (long long)base0 * KVH) / cw.r.U);
   cw.seq0 = (long long)base0 * KVH + (long long)cw.h * cw.r.U;
   cw.blk = 0;
 
   // ---- fetch side: this warp's units are the partition-local indices w, w + TG, ..; the cursor below runs NS units
-  // ahead of the compute loop. The common case (next unit in the same sequence, its page id already in the warp's
-  // 32-entry window) costs a shuffle, one 64-bit multiply-add and the copy instructions of one lane.
+  // ahead of the compute loop. The common case (next unit in the same sequence, its page ids already in the warp's
+  // 32-entry window) costs a shuffle per 16 tokens, one 64-bit multiply-add and the copy instructions of UB lanes.
   const int n_my = n_units > w ? (n_units - w + TG - 1) / TG : 0;
-  uint8_t* my_ring = ring + w * NS * Gm::STAGE;
-  uint64_t* my_bars = bars + w * NS;
+  // shared-memory addresses of this warp's ring and barriers, and the byte offsets of this lane's rows and blocks
+  // inside a stage. They are constant for the whole kernel; passing them through an empty asm keeps the compiler from
+  // re-deriving them from the thread index inside the main loop.
+  uint32_t ring_a = smem_u32(ring + w * NS * Gm::STAGE), bars_a = smem_u32(bars + w * NS);
+  const int r0 = Gm::tok(g), r1 = Gm::tok(g + 8);
+  const int t00 = Gm::tok(2 * c), t01 = Gm::tok(2 * c + 1), t10 = Gm::tok(2 * c + 8), t11 = Gm::tok(2 * c + 9);
+  uint32_t koff_d = r0 * Gm::ROW + 8 * Gm::kblk(c, 0), koff_s = Gm::SF_BASE + r0 * Gm::SF_ROW + Gm::kblk(c, 0);
+  uint32_t voff_d = Gm::TILE + t00 * Gm::ROW + 8 * g, voff_s = Gm::TILE + Gm::SF_BASE + t00 * Gm::SF_ROW + g;
+  asm volatile("" : "+r"(ring_a), "+r"(bars_a), "+r"(koff_d), "+r"(koff_s), "+r"(voff_d), "+r"(voff_s));
+  constexpr int KR1 = (D == 128 && LAYOUT == 0) ? 1 : 8;                  // r1 - r0
+  constexpr int VR01 = (D == 128 && LAYOUT == 0) ? 2 : 1, VR10 = (D == 128 && LAYOUT == 0) ? 1 : 8,
+                VR11 = (D == 128 && LAYOUT == 0) ? 3 : 9;                 // t01 - t00, t10 - t00, t11 - t00
+
   int f_b = cw.b, f_h = cw.h, f_U = cw.r.U, f_L = cw.r.L;
-  int f_blk = w + (int)(lo - cw.seq0);              // block (inside the cursor's sequence) of the next unit; may run past
-  int f_fast_end = 0;                               // blocks below this bound take the fast path
-  int f_idx = 0, pg = 0;                            // page ids of the warp's next 32 units of the sequence, one per lane
-  int f_n = 0, f_left = n_my;                       // stages used so far, units still to be fetched
+  int f_blk = w + (int)(lo - cw.seq0);              // unit (inside the cursor's sequence) to fetch next; may run past
+  int f_fast_end = 0;                               // units below this bound take the fast path
+  int f_idx = 0, pg = 0;                            // page ids of the warp's next 32 blocks of the sequence, one per lane
+  unsigned f_n = 0;                                 // stages used so far
+  int f_left = n_my;                                // units still to be fetched
   const uint8_t* f_k = p.kd + (long long)f_h * p.dsh;
   const uint8_t* f_v = p.vd + (long long)f_h * p.dsh;
   const uint8_t* f_ks = p.ksf + (long long)f_h * p.ssh;
@@ -247,7 +267,7 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
         if (++f_h == KVH) {
           f_h = 0;
           ReqInfo r;
-          do { r = load_req(p, ++f_b); } while (r.U == 0);
+          do { r = load_req<LOG_UT>(p, ++f_b); } while (r.U == 0);
           f_U = r.U;
           f_L = r.L;
         }
@@ -259,38 +279,45 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
       f_bt = p.bt + (long long)f_b * p.MP;
     }
     if (f_L == 0) {                                 // an empty context has one unit and nothing to read: complete the
-      if (lane == 0) mbar_arrive(my_bars + f_n % NS);   // stage's phase with a plain arrival so that both sides stay in step
+      if (lane == 0) mbar_arrive_u32(bars_a + 8 * (f_n % NS));   // phase with a plain arrival so that both sides stay in step
       f_fast_end = 0;
       return true;
     }
-    const int blk_l = f_blk + lane * TG;            // refill the page window from the current block
-    pg = blk_l < f_U ? __ldg(f_bt + ((blk_l * 16) >> lps)) : 0;
+    // refill the page window from the current unit: lane j holds the page of 16-token block j % UB of the warp's
+    // (j / UB)-th next unit
+    const int tok_l = (f_blk + (lane / UB) * TG) * UT + (lane % UB) * 16;
+    pg = tok_l < f_L ? __ldg(f_bt + (tok_l >> lps)) : 0;
     f_idx = 0;
-    f_fast_end = min(f_U, f_blk + 32 * TG);
+    f_fast_end = min(f_U, f_blk + (32 / UB) * TG);
     return false;
   };
   auto fetch_one = [&]() {
     bool empty = false;
     if (f_blk >= f_fast_end) empty = fetch_slow();
     if (!empty) {
-      const int page = __shfl_sync(0xffffffffu, pg, f_idx);
-      ++f_idx;
-      if (lane == 0) {
-        const int pos0 = (f_blk * 16) & (p.PS - 1);
-        const int slot = f_n % NS;
-        uint8_t* st = my_ring + slot * Gm::STAGE;
-        uint64_t* bar = my_bars + slot;
-        mbar_expect_tx(bar, Gm::STAGE);
+      const int page = __shfl_sync(0xffffffffu, pg, f_idx + (lane < UB ? lane : 0));
+      f_idx += UB;
+      const int tok0 = f_blk * UT;
+      const int nb = min(UB, (f_L - tok0 + 15) >> 4);          // 16-token blocks of this unit that exist
+      const unsigned slot = f_n % NS;
+      const uint32_t bar = bars_a + 8 * slot;
+      if (lane == 0) mbar_expect_tx_u32(bar, nb * (Gm::STAGE / UB));
+      __syncwarp();
+      if (lane < nb) {                                          // lane j copies block j of the unit
+        const int pos0 = (tok0 + 16 * lane) & (p.PS - 1);
         const long long doff = (long long)page * p.dsp + (long long)pos0 * p.dst;
         if (LAYOUT == 0) {
-          bulk_g2s(st, f_k + doff, Gm::TILE, bar);
-          bulk_g2s(st + Gm::TILE, f_v + doff, Gm::TILE, bar);
+          const uint32_t st = ring_a + slot * Gm::STAGE + lane * (16 * Gm::SLOT);
+          bulk_g2s_u32(st, f_k + doff, 16 * Gm::SLOT, bar);
+          bulk_g2s_u32(st + Gm::TILE, f_v + doff, 16 * Gm::SLOT, bar);
         } else {
           const long long soff = (long long)page * p.ssp + (long long)pos0 * p.sst;
-          bulk_g2s(st, f_k + doff, 16 * Gm::SD, bar);
-          bulk_g2s(st + 16 * Gm::SD, f_ks + soff, 16 * Gm::SS, bar);
-          bulk_g2s(st + Gm::TILE, f_v + doff, 16 * Gm::SD, bar);
-          bulk_g2s(st + Gm::TILE + 16 * Gm::SD, f_vs + soff, 16 * Gm::SS, bar);
+          const uint32_t st = ring_a + slot * Gm::STAGE + lane * (16 * Gm::SD);
+          const uint32_t ss = ring_a + slot * Gm::STAGE + UT * Gm::SD + lane * (16 * Gm::SS);
+          bulk_g2s_u32(st, f_k + doff, 16 * Gm::SD, bar);
+          bulk_g2s_u32(ss, f_ks + soff, 16 * Gm::SS, bar);
+          bulk_g2s_u32(st + Gm::TILE, f_v + doff, 16 * Gm::SD, bar);
+          bulk_g2s_u32(ss + Gm::TILE, f_vs + soff, 16 * Gm::SS, bar);
         }
       }
     }
@@ -299,18 +326,9 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
     --f_left;
   };
 
-  int c_n = 0;                                      // stages consumed so far
+  unsigned c_n = 0;                                 // stages consumed so far
   bool dead = false;                                // a bounded wait ran out: stop consuming
   while (f_n < NS && f_left > 0) fetch_one();
-
-  // byte offsets of this lane's rows and blocks inside a stage (constant for the whole kernel)
-  const int r0 = Gm::tok(g), r1 = Gm::tok(g + 8);
-  const int t00 = Gm::tok(2 * c), t01 = Gm::tok(2 * c + 1), t10 = Gm::tok(2 * c + 8), t11 = Gm::tok(2 * c + 9);
-  const int koff_d = r0 * Gm::ROW + 8 * Gm::kblk(c, 0), koff_s = Gm::SF_BASE + r0 * Gm::SF_ROW + Gm::kblk(c, 0);
-  const int voff_d = Gm::TILE + t00 * Gm::ROW + 8 * g, voff_s = Gm::TILE + Gm::SF_BASE + t00 * Gm::SF_ROW + g;
-  constexpr int KR1 = (D == 128 && LAYOUT == 0) ? 1 : 8;                  // r1 - r0
-  constexpr int VR01 = (D == 128 && LAYOUT == 0) ? 2 : 1, VR10 = (D == 128 && LAYOUT == 0) ? 1 : 8,
-                VR11 = (D == 128 && LAYOUT == 0) ? 3 : 9;                 // t01 - t00, t10 - t00, t11 - t00
 
   // ---- compute side: walk the pieces of the partition
   long long pos = lo;
@@ -334,7 +352,7 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
       descs[part] = d;
     }
 
-    // this warp's blocks of the piece: blk_first, blk_first + TG, .. < blk_end
+    // this warp's units of the piece: blk_first, blk_first + TG, .. < blk_end
     const int blk_first = blk0 + ((w - k0) % TG + TG) % TG, blk_end = blk0 + n_piece;
     // running max (raw score units) and sum of query rows 2c and 2c+1 over this lane's tokens
     float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;
@@ -375,14 +393,14 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
       }
       // visible context of query rows 2c, 2c+1 (causal among the request's own query tokens)
       const int lim0 = 2 * c < R ? L - ql + (2 * c) / G + 1 : L, lim1 = 2 * c + 1 < R ? L - ql + (2 * c + 1) / G + 1 : L;
-      const int blk_mask = (L - ql + 1) >> 4;        // blocks below this one are visible to every query row in full
+      const int blk_mask = (L - ql + 1) >> LOG_UT;   // units below this one are visible to every query row in full
       float mneg0 = -m0 * sc, mneg1 = -m1 * sc;      // p = 2^(s * sc + mneg)
       float thr0 = m0 + tau_raw, thr1 = m1 + tau_raw;
 
       for (int blk = blk_first; blk < blk_end; blk += TG) {
-        const int slot = c_n % NS;
-        if (!mbar_try_wait(my_bars + slot, (c_n / NS) & 1)) {
-          if (!mbar_wait_bounded(my_bars + slot, (c_n / NS) & 1)) {
+        const unsigned slot = c_n % NS;
+        if (!mbar_try_wait_u32(bars_a + 8 * slot, (c_n / NS) & 1)) {
+          if (!mbar_wait_bounded_u32(bars_a + 8 * slot, (c_n / NS) & 1)) {
             if (lane == 0) atomicExch(&hdr->status, HKV_ERR_DEVICE_WAIT);
             dead = true;
             break;
@@ -390,55 +408,67 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
         }
         ++c_n;
         if (L > 0) {                                  // (the single unit of an empty context carries nothing)
-          const uint8_t* st = my_ring + slot * Gm::STAGE;
-          const uint8_t* kd_ = st + koff_d;
-          const uint8_t* ks_ = st + koff_s;
-          const uint8_t* vd_ = st + voff_d;
-          const uint8_t* vs_ = st + voff_s;
-          const bool masked = blk >= blk_mask;        // warp-uniform: only the last block(s) of a sequence
+          const uint32_t st = ring_a + slot * Gm::STAGE;
+          const uint32_t kd_ = st + koff_d, ks_ = st + koff_s, vd_ = st + voff_d, vs_ = st + voff_s;
+          const bool masked = blk >= blk_mask;        // warp-uniform: only the last unit(s) of a sequence
 
-          // ---------------- S^T = K Q^T : rows = the 16 tokens, columns = query rows; two accumulators so that
-          // consecutive mma do not wait for each other
-          float sa0[4] = {0.f, 0.f, 0.f, 0.f}, sa1[4] = {0.f, 0.f, 0.f, 0.f};
+          // ---------------- S^T = K Q^T per 16-token block: rows = tokens, columns = query rows
+          float x[UB][4];
 #pragma unroll
-          for (int u = 0; u < Gm::NBL; ++u) {
-            constexpr int dummy = 0;
-            (void)dummy;
-            const int du = 8 * (Gm::kblk(0, u) - Gm::kblk(0, 0)), su = Gm::kblk(0, u) - Gm::kblk(0, 0);
-            const uint2 w0 = *reinterpret_cast<const uint2*>(kd_ + du);
-            const uint2 w1 = *reinterpret_cast<const uint2*>(kd_ + du + KR1 * Gm::ROW);
-            const uint32_t f0 = ks_[su], f1 = ks_[su + KR1 * Gm::SF_ROW];
-            const __half2 sf = u32_as_h2(e4m3x2_to_f16x2(f0 | (f1 << 8)));     // (scale of row r0, scale of row r1)
-            const __half2 sf0 = __low2half2(sf), sf1 = __high2half2(sf);
-            uint32_t e0[4], e1[4], e2[4], e3[4];
-            e2m1x8_to_f16x2(w0.x, e0);
-            e2m1x8_to_f16x2(w0.y, e1);
-            e2m1x8_to_f16x2(w1.x, e2);
-            e2m1x8_to_f16x2(w1.y, e3);
-            // k-step v of this block: A = {row r0 k-low, row r1 k-low, row r0 k-high, row r1 k-high}
-            mma_f16(sa0, hmul2h(e0[0], sf0), hmul2h(e2[0], sf1), hmul2h(e0[1], sf0), hmul2h(e2[1], sf1), qa[4 * u + 0][0],
-                    qa[4 * u + 0][1]);
-            mma_f16(sa1, hmul2h(e0[2], sf0), hmul2h(e2[2], sf1), hmul2h(e0[3], sf0), hmul2h(e2[3], sf1), qa[4 * u + 1][0],
-                    qa[4 * u + 1][1]);
-            mma_f16(sa0, hmul2h(e1[0], sf0), hmul2h(e3[0], sf1), hmul2h(e1[1], sf0), hmul2h(e3[1], sf1), qa[4 * u + 2][0],
-                    qa[4 * u + 2][1]);
-            mma_f16(sa1, hmul2h(e1[2], sf0), hmul2h(e3[2], sf1), hmul2h(e1[3], sf0), hmul2h(e3[3], sf1), qa[4 * u + 3][0],
-                    qa[4 * u + 3][1]);
+          for (int bi = 0; bi < UB; ++bi) {
+            float sa[Gm::NCH][4];
+#pragma unroll
+            for (int i = 0; i < Gm::NCH; ++i) sa[i][0] = sa[i][1] = sa[i][2] = sa[i][3] = 0.0f;
+#pragma unroll
+            for (int u = 0; u < Gm::NBL; ++u) {
+              const int du = bi * 16 * Gm::ROW + 8 * (Gm::kblk(0, u) - Gm::kblk(0, 0));
+              const int su = bi * 16 * Gm::SF_ROW + Gm::kblk(0, u) - Gm::kblk(0, 0);
+              const uint2 w0 = lds64(kd_ + du);
+              const uint2 w1 = lds64(kd_ + du + KR1 * Gm::ROW);
+              const uint32_t f0 = lds8(ks_ + su), f1 = lds8(ks_ + su + KR1 * Gm::SF_ROW);
+              const __half2 sf = u32_as_h2(e4m3x2_to_f16x2(f0 | (f1 << 8)));   // (scale of row r0, scale of row r1)
+              const __half2 sf0 = __low2half2(sf), sf1 = __high2half2(sf);
+              uint32_t e0[4], e1[4], e2[4], e3[4];
+              e2m1x8_to_f16x2(w0.x, e0);
+              e2m1x8_to_f16x2(w0.y, e1);
+              e2m1x8_to_f16x2(w1.x, e2);
+              e2m1x8_to_f16x2(w1.y, e3);
+              // k-step v of this block: A = {row r0 k-low, row r1 k-low, row r0 k-high, row r1 k-high}
+              mma_f16(sa[0], hmul2h(e0[0], sf0), hmul2h(e2[0], sf1), hmul2h(e0[1], sf0), hmul2h(e2[1], sf1),
+                      qa[4 * u + 0][0], qa[4 * u + 0][1]);
+              mma_f16(sa[Gm::NCH - 1], hmul2h(e0[2], sf0), hmul2h(e2[2], sf1), hmul2h(e0[3], sf0), hmul2h(e2[3], sf1),
+                      qa[4 * u + 1][0], qa[4 * u + 1][1]);
+              mma_f16(sa[0], hmul2h(e1[0], sf0), hmul2h(e3[0], sf1), hmul2h(e1[1], sf0), hmul2h(e3[1], sf1),
+                      qa[4 * u + 2][0], qa[4 * u + 2][1]);
+              mma_f16(sa[Gm::NCH - 1], hmul2h(e1[2], sf0), hmul2h(e3[2], sf1), hmul2h(e1[3], sf0), hmul2h(e3[3], sf1),
+                      qa[4 * u + 3][0], qa[4 * u + 3][1]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x[bi][i] = Gm::NCH == 2 ? sa[0][i] + sa[Gm::NCH - 1][i] : sa[0][i];
           }
 
           // ---------------- online softmax (raw score units): this lane holds query rows 2c, 2c+1 of tokens r0, r1
-          float x00 = sa0[0] + sa1[0], x01 = sa0[1] + sa1[1], x10 = sa0[2] + sa1[2], x11 = sa0[3] + sa1[3];
+          // of every block; x[bi] = {(r0, row 2c), (r0, row 2c+1), (r1, row 2c), (r1, row 2c+1)}
+          const int tbase = blk * UT;
           if (masked) {
             const float ninf = -__int_as_float(0x7f800000);
-            const int tbase = blk * 16;
-            x00 = tbase + r0 < lim0 ? x00 : ninf;
-            x01 = tbase + r0 < lim1 ? x01 : ninf;
-            x10 = tbase + r1 < lim0 ? x10 : ninf;
-            x11 = tbase + r1 < lim1 ? x11 : ninf;
+#pragma unroll
+            for (int bi = 0; bi < UB; ++bi) {
+              const int ta = tbase + 16 * bi + r0, tb = tbase + 16 * bi + r1;
+              x[bi][0] = ta < lim0 ? x[bi][0] : ninf;
+              x[bi][1] = ta < lim1 ? x[bi][1] : ninf;
+              x[bi][2] = tb < lim0 ? x[bi][2] : ninf;
+              x[bi][3] = tb < lim1 ? x[bi][3] : ninf;
+            }
           }
           // the running max moves only when some score exceeds it by more than TAU (then P stays below 2^TAU, inside
           // f16); the cross-lane maximum is needed only in that case
-          float bm0 = fmaxf(x00, x10), bm1 = fmaxf(x01, x11);
+          float bm0 = fmaxf(x[0][0], x[0][2]), bm1 = fmaxf(x[0][1], x[0][3]);
+#pragma unroll
+          for (int bi = 1; bi < UB; ++bi) {
+            bm0 = fmaxf(bm0, fmaxf(x[bi][0], x[bi][2]));
+            bm1 = fmaxf(bm1, fmaxf(x[bi][1], x[bi][3]));
+          }
           if (__any_sync(0xffffffffu, (bm0 > thr0) | (bm1 > thr1))) {
 #pragma unroll
             for (int of = 4; of < 32; of <<= 1) {
@@ -456,47 +486,57 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
               o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1;
             }
           }
-          const float p00 = fast_exp2(fmaf(x00, sc, mneg0)), p01 = fast_exp2(fmaf(x01, sc, mneg1)),
-                      p10 = fast_exp2(fmaf(x10, sc, mneg0)), p11 = fast_exp2(fmaf(x11, sc, mneg1));
-          l0 += p00 + p10;
-          l1 += p01 + p11;
-          // P^T as the B operand of the second product: transpose the two 8x8 (token, row) tiles
-          const uint32_t pb0 = movmatrix_trans(pack_f16x2(p00, p01)), pb1 = movmatrix_trans(pack_f16x2(p10, p11));
+          uint32_t pb[UB][2];                         // P^T as the B operand of the second product
+#pragma unroll
+          for (int bi = 0; bi < UB; ++bi) {
+            const float p00 = fast_exp2(fmaf(x[bi][0], sc, mneg0)), p01 = fast_exp2(fmaf(x[bi][1], sc, mneg1)),
+                        p10 = fast_exp2(fmaf(x[bi][2], sc, mneg0)), p11 = fast_exp2(fmaf(x[bi][3], sc, mneg1));
+            l0 += p00 + p10;
+            l1 += p01 + p11;
+            // transpose the two 8x8 (token, row) tiles
+            pb[bi][0] = movmatrix_trans(pack_f16x2(p00, p01));
+            pb[bi][1] = movmatrix_trans(pack_f16x2(p10, p11));
+          }
 
           // ---------------- O^T += V^T P^T : rows = channels of block g (+8), columns = query rows
+          const int nvalid = L - tbase;               // >= UT unless this is the sequence's last unit
 #pragma unroll
-          for (int hf = 0; hf < Gm::NH; ++hf) {
-            const uint2 v00 = *reinterpret_cast<const uint2*>(vd_ + 64 * hf);
-            const uint2 v01 = *reinterpret_cast<const uint2*>(vd_ + 64 * hf + VR01 * Gm::ROW);
-            const uint2 v10 = *reinterpret_cast<const uint2*>(vd_ + 64 * hf + VR10 * Gm::ROW);
-            const uint2 v11 = *reinterpret_cast<const uint2*>(vd_ + 64 * hf + VR11 * Gm::ROW);
-            uint32_t f00 = vs_[8 * hf], f01 = vs_[8 * hf + VR01 * Gm::SF_ROW];
-            uint32_t f10 = vs_[8 * hf + VR10 * Gm::SF_ROW], f11 = vs_[8 * hf + VR11 * Gm::SF_ROW];
-            if (masked) {                             // rows past the context hold arbitrary bytes: read them as 0
-              const int nvalid = L - blk * 16;
-              f00 = t00 < nvalid ? f00 : 0u;
-              f01 = t01 < nvalid ? f01 : 0u;
-              f10 = t10 < nvalid ? f10 : 0u;
-              f11 = t11 < nvalid ? f11 : 0u;
-            }
-            const __half2 sa = u32_as_h2(e4m3x2_to_f16x2(f00 | (f01 << 8))), sb = u32_as_h2(e4m3x2_to_f16x2(f10 | (f11 << 8)));
-            const uint32_t M = 0x0f0f0f0fu;
+          for (int bi = 0; bi < UB; ++bi) {
 #pragma unroll
-            for (int wv = 0; wv < 2; ++wv) {
-              const uint32_t a0 = wv ? v00.y : v00.x, a1 = wv ? v01.y : v01.x, b0_ = wv ? v10.y : v10.x,
-                             b1_ = wv ? v11.y : v11.x;
-              // bytes of (token pair, channel): low nibble = first token of the pair, high nibble = second
-              const uint32_t xe = (a0 & M) | ((a1 * 16u) & ~M), xo = ((a0 >> 4) & M) | (a1 & ~M);
-              const uint32_t ye = (b0_ & M) | ((b1_ * 16u) & ~M), yo = ((b0_ >> 4) & M) | (b1_ & ~M);
-              uint32_t ae[4], ao[4], be[4], bo[4];   // [channel pair] -> f16x2 over (first, second) token
-              e2m1x8_to_f16x2(xe, ae);
-              e2m1x8_to_f16x2(xo, ao);
-              e2m1x8_to_f16x2(ye, be);
-              e2m1x8_to_f16x2(yo, bo);
+            for (int hf = 0; hf < Gm::NH; ++hf) {
+              const int dv = bi * 16 * Gm::ROW + 64 * hf, sv = bi * 16 * Gm::SF_ROW + 8 * hf;
+              const uint2 v00 = lds64(vd_ + dv);
+              const uint2 v01 = lds64(vd_ + dv + VR01 * Gm::ROW);
+              const uint2 v10 = lds64(vd_ + dv + VR10 * Gm::ROW);
+              const uint2 v11 = lds64(vd_ + dv + VR11 * Gm::ROW);
+              uint32_t f00 = lds8(vs_ + sv), f01 = lds8(vs_ + sv + VR01 * Gm::SF_ROW);
+              uint32_t f10 = lds8(vs_ + sv + VR10 * Gm::SF_ROW), f11 = lds8(vs_ + sv + VR11 * Gm::SF_ROW);
+              if (masked) {                           // rows past the context hold arbitrary bytes: read them as 0
+                f00 = 16 * bi + t00 < nvalid ? f00 : 0u;
+                f01 = 16 * bi + t01 < nvalid ? f01 : 0u;
+                f10 = 16 * bi + t10 < nvalid ? f10 : 0u;
+                f11 = 16 * bi + t11 < nvalid ? f11 : 0u;
+              }
+              const __half2 sa = u32_as_h2(e4m3x2_to_f16x2(f00 | (f01 << 8))),
+                            sb = u32_as_h2(e4m3x2_to_f16x2(f10 | (f11 << 8)));
+              const uint32_t M = 0x0f0f0f0fu;
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                mma_f16(o[8 * hf + 4 * wv + i], hmul2h(ae[i], sa), hmul2h(ao[i], sa), hmul2h(be[i], sb), hmul2h(bo[i], sb),
-                        pb0, pb1);
+              for (int wv = 0; wv < 2; ++wv) {
+                const uint32_t a0 = wv ? v00.y : v00.x, a1 = wv ? v01.y : v01.x, b0_ = wv ? v10.y : v10.x,
+                               b1_ = wv ? v11.y : v11.x;
+                // bytes of (token pair, channel): low nibble = first token of the pair, high nibble = second
+                const uint32_t xe = (a0 & M) | ((a1 * 16u) & ~M), xo = ((a0 >> 4) & M) | (a1 & ~M);
+                const uint32_t ye = (b0_ & M) | ((b1_ * 16u) & ~M), yo = ((b0_ >> 4) & M) | (b1_ & ~M);
+                uint32_t ae[4], ao[4], be[4], bo[4]; // [channel pair] -> f16x2 over (first, second) token
+                e2m1x8_to_f16x2(xe, ae);
+                e2m1x8_to_f16x2(xo, ao);
+                e2m1x8_to_f16x2(ye, be);
+                e2m1x8_to_f16x2(yo, bo);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  mma_f16(o[8 * hf + 4 * wv + i], hmul2h(ae[i], sa), hmul2h(ao[i], sa), hmul2h(be[i], sb),
+                          hmul2h(bo[i], sb), pb[bi][0], pb[bi][1]);
+              }
             }
           }
           __syncwarp();
@@ -566,7 +606,7 @@ __global__ void __launch_bounds__(NTHREADS, D == 128 ? 4 : 2) decode_kernel(cons
   // a warp that gave up may still have copies in flight: wait for them (bounded) before the CTA's shared memory is
   // released
   if (dead) {
-    for (int i = c_n; i < f_n; ++i) (void)mbar_wait_bounded(my_bars + i % NS, (i / NS) & 1);
+    for (unsigned i = c_n; i < f_n; ++i) (void)mbar_wait_bounded_u32(bars_a + 8 * (i % NS), (i / NS) & 1);
   }
 }
 
@@ -626,17 +666,11 @@ struct DeviceInfo {
 static DeviceInfo g_dev[64];
 
 template <int D, int LAYOUT>
-struct Pick {
-  static constexpr int NS = 4;                       // stages per warp (a power of two keeps the slot arithmetic cheap)
-};
-
-template <int D, int LAYOUT>
 static cudaError_t setup_variant(int& ctas) {
-  constexpr int NS = Pick<D, LAYOUT>::NS;
-  auto k = decode_kernel<D, LAYOUT, NS>;
-  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D, LAYOUT, NS>::TOTAL);
+  auto k = decode_kernel<D, LAYOUT>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D, LAYOUT>::TOTAL);
   if (e != cudaSuccess) return e;
-  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, k, NTHREADS, Smem<D, LAYOUT, NS>::TOTAL);
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, k, NTHREADS, Smem<D, LAYOUT>::TOTAL);
 }
 
 static int device_info(DeviceInfo** out) {
@@ -729,8 +763,7 @@ extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const 
   p.v_scale = v_scale;
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned grid = (unsigned)n_parts;
-#define HKV_LAUNCH(DD, LL)                                                                                  \
-  decode_kernel<DD, LL, Pick<DD, LL>::NS><<<grid, NTHREADS, Smem<DD, LL, Pick<DD, LL>::NS>::TOTAL, st>>>(p)
+#define HKV_LAUNCH(DD, LL) decode_kernel<DD, LL><<<grid, NTHREADS, Smem<DD, LL>::TOTAL, st>>>(p)
   if (D == 128) {
     if (layout == 0) HKV_LAUNCH(128, 0); else HKV_LAUNCH(128, 1);
   } else {
