@@ -130,6 +130,10 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   float* lse_ws = reinterpret_cast<float*>(p.ws + wl.lse_off);
   float* opart_ws = reinterpret_cast<float*>(p.ws + wl.opart_off);
 
+  if (tid < TG * NS) mbar_init(bars + tid, 1);
+  pdl_wait();                                     // every global input may come from the preceding launch
+  pdl_launch_dependents();
+
   // ---- coarse prefix of units per request: coarse[k] = sum of U_b over b < 32 k
   const int ngrp = (B + 31) >> 5;
   for (int grp = w; grp < ngrp; grp += TG) {
@@ -139,7 +143,6 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
     for (int o = 16; o > 0; o >>= 1) u += __shfl_xor_sync(0xffffffffu, u, o);
     if (lane == 0) coarse[grp + 1] = u;
   }
-  if (tid < TG * NS) mbar_init(bars + tid, 1);
   __syncthreads();
   if (w == 0) {                                   // scan of up to kMaxBatch / 32 group sums
     const int per_lane = (ngrp + 31) >> 5;
@@ -618,7 +621,9 @@ template <int D>
 __global__ void __launch_bounds__(128) combine_kernel(const uint8_t* ws, const int* qsl, __nv_bfloat16* out, int KVH,
                                                       int G, int qlmax, float v_scale) {
   const int part = blockIdx.x, tid = threadIdx.x;
-  const int n_parts = reinterpret_cast<const Header*>(ws)->n_parts;   // written by the preceding decode launch
+  pdl_wait();                                     // the workspace is written by the preceding decode launch
+  pdl_launch_dependents();
+  const int n_parts = reinterpret_cast<const Header*>(ws)->n_parts;
   if (part >= n_parts) return;
   const WorkspaceLayout wl(n_parts, RPAD, D);
   const PartDesc d = reinterpret_cast<const PartDesc*>(ws + wl.desc_off)[part];
@@ -763,14 +768,11 @@ extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const 
   p.v_scale = v_scale;
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned grid = (unsigned)n_parts;
-#define HKV_LAUNCH(DD, LL) decode_kernel<DD, LL><<<grid, NTHREADS, Smem<DD, LL>::TOTAL, st>>>(p)
-  if (D == 128) {
-    if (layout == 0) HKV_LAUNCH(128, 0); else HKV_LAUNCH(128, 1);
-  } else {
-    if (layout == 0) HKV_LAUNCH(256, 0); else HKV_LAUNCH(256, 1);
-  }
-#undef HKV_LAUNCH
-  return record_cuda(cudaGetLastError());
+  void (*k)(const DecodeParams) = D == 128 ? (layout == 0 ? decode_kernel<128, 0> : decode_kernel<128, 1>)
+                                           : (layout == 0 ? decode_kernel<256, 0> : decode_kernel<256, 1>);
+  const size_t smem_bytes = D == 128 ? (size_t)Smem<128, 0>::TOTAL : (size_t)Smem<256, 0>::TOTAL;
+  static_assert(Smem<128, 0>::TOTAL == Smem<128, 1>::TOTAL && Smem<256, 0>::TOTAL == Smem<256, 1>::TOTAL, "layouts share a size");
+  return record_cuda(launch_pdl(k, dim3(grid), dim3(NTHREADS), smem_bytes, st, p));
 }
 
 extern "C" int hkv_combine(const void* workspace, size_t workspace_bytes, const int32_t* query_start_loc, int B,
@@ -791,13 +793,10 @@ extern "C" int hkv_combine(const void* workspace, size_t workspace_bytes, const 
   const unsigned grid = (unsigned)max_parts(*di, D);
   if (workspace_bytes < WorkspaceLayout(1, RPAD, D).total) return HKV_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
-  if (D == 128)
-    combine_kernel<128><<<grid, 128, 0, st>>>((const uint8_t*)workspace, query_start_loc, (__nv_bfloat16*)out, KVH, G,
-                                              qlmax, v_scale);
-  else
-    combine_kernel<256><<<grid, 128, 0, st>>>((const uint8_t*)workspace, query_start_loc, (__nv_bfloat16*)out, KVH, G,
-                                              qlmax, v_scale);
-  return record_cuda(cudaGetLastError());
+  void (*k)(const uint8_t*, const int*, __nv_bfloat16*, int, int, int, float) =
+      D == 128 ? combine_kernel<128> : combine_kernel<256>;
+  return record_cuda(launch_pdl(k, dim3(grid), dim3(128), 0, st, (const uint8_t*)workspace, (const int*)query_start_loc,
+                                (__nv_bfloat16*)out, KVH, G, qlmax, v_scale));
 }
 
 extern "C" int hkv_workspace_status(void* workspace, int* status, void* stream) {

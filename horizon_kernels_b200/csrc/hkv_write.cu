@@ -1,9 +1,9 @@
 // Quantize-on-write for the NVFP4 paged KV cache (sm_100a).
 //
-// One thread owns one block of 16 consecutive channels of one (token, kv head, side): it reads 32 bytes of bf16,
-// picks the E4M3 block scale (optionally by the 4-candidate squared-error search), encodes 16 E2M1 codes and stores
-// 8 code bytes + 1 scale byte at slot = page * PS + position. Threads of a warp cover consecutive blocks, so global
-// reads are 1 KiB per warp and the code stores 256 contiguous bytes per (token, head, side) row.
+// Four threads own one block of 16 consecutive channels of one (token, kv head, side): they read its 32 bytes of
+// bf16, pick the E4M3 block scale (optionally by the 4-candidate squared-error search, one candidate per thread),
+// encode the 16 E2M1 codes and store 8 code bytes + 1 scale byte at slot = page * PS + position. Consecutive quads cover
+// consecutive blocks, so a warp reads 256 contiguous bytes and stores 64 contiguous code bytes.
 //
 // Bit-exactness: the result must equal the reference's PyTorch quantiser (kv_fp4_ref.py:159-186 `quantize_rows`,
 // rules at kv_fp4_ref.py:15-25) byte for byte. Every arithmetic step is therefore a single IEEE fp32 operation issued
@@ -64,14 +64,22 @@ __device__ __forceinline__ float block_sse(const float (&ax)[16], float s) {
   return acc;
 }
 
+// Four lanes share one block of 16 values: every lane reads the whole block (the four identical 16-byte requests of
+// a quad are served by one access), lane k of the quad scores scale candidate k, the quad agrees on the winner with
+// shuffles in candidate order (strict "<", so the earliest candidate wins a tie, as in the reference), and every lane
+// encodes 4 of the 16 values. One (token, kv head, side) row of D values is 4 * D / 16 consecutive threads.
 template <int D, int SEARCH>
 __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   constexpr int NB = D / 16;                      // blocks per row
+  pdl_wait();                                     // inputs and the cache may come from the preceding launch
+  pdl_launch_dependents();
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int cand = (int)(gid & 3);
+  const long long bid = gid >> 2;
   const int per_tok = 2 * p.KVH * NB;
-  const long long t = gid / per_tok;
-  if (t >= p.n_slots) return;
-  const int rem = (int)(gid - t * per_tok);
+  const long long t = bid / per_tok;
+  if (t >= p.n_slots) return;                     // uniform per quad: a quad never straddles two tokens
+  const int rem = (int)(bid - t * per_tok);
   const int side = rem / (p.KVH * NB);
   const int hb = rem - side * (p.KVH * NB);
   const int h = hb / NB, blk = hb - h * NB;
@@ -83,45 +91,46 @@ __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   const uint4 w1 = *reinterpret_cast<const uint4*>(src + blk * 16 + 8);
   const uint32_t ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
   float ax[16];
-  unsigned neg = 0;                               // bit i: x_i < 0 (false for -0.0, as in the reference)
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const float lo = __uint_as_float(ws[i] << 16), hi = __uint_as_float(ws[i] & 0xffff0000u);
-    neg |= (lo < 0.0f ? 1u : 0u) << (2 * i);
-    neg |= (hi < 0.0f ? 1u : 0u) << (2 * i + 1);
-    ax[2 * i] = fabsf(lo);
-    ax[2 * i + 1] = fabsf(hi);
+    ax[2 * i] = fabsf(__uint_as_float(ws[i] << 16));
+    ax[2 * i + 1] = fabsf(__uint_as_float(ws[i] & 0xffff0000u));
     amax = fmaxf(amax, fmaxf(ax[2 * i], ax[2 * i + 1]));
   }
   const float g = side ? p.gv[h] : p.gk[h];
-  unsigned cb = e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 6.0f)));
+  const int c0 = (int)e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 6.0f)));
+  int cb = c0;
   if (SEARCH) {
-    const int c0 = (int)cb;
-    const unsigned cand[3] = {(unsigned)min(c0 + 1, 126), (unsigned)max(c0 - 1, 0),
-                              e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 4.0f)))};
-    float best = block_sse(ax, __fmul_rn(e4m3_dec(cb), g));
-#pragma unroll 1
-    for (int k = 0; k < 3; ++k) {
-      const float e = block_sse(ax, __fmul_rn(e4m3_dec(cand[k]), g));
-      if (e < best) {
-        best = e;
-        cb = cand[k];
+    const int cc = cand == 0 ? c0 : cand == 1 ? min(c0 + 1, 126) : cand == 2 ? max(c0 - 1, 0)
+                 : (int)e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 4.0f)));
+    const float err = block_sse(ax, __fmul_rn(e4m3_dec((unsigned)cc), g));
+    const int lane0 = (threadIdx.x & 31) & ~3;
+    float best = __shfl_sync(0xffffffffu, err, lane0);
+    cb = __shfl_sync(0xffffffffu, cc, lane0);
+#pragma unroll
+    for (int k = 1; k < 4; ++k) {
+      const float ek = __shfl_sync(0xffffffffu, err, lane0 + k);
+      const int ck = __shfl_sync(0xffffffffu, cc, lane0 + k);
+      if (ek < best) {
+        best = ek;
+        cb = ck;
       }
     }
   }
-  const float s = __fmul_rn(e4m3_dec(cb), g);
-  uint32_t lo = 0, hi = 0;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    lo |= (mag_of(ax[i], s) | (((neg >> i) & 1u) << 3)) << (4 * i);
-    hi |= (mag_of(ax[8 + i], s) | (((neg >> (8 + i)) & 1u) << 3)) << (4 * i);
-  }
+  const float s = __fmul_rn(e4m3_dec((unsigned)cb), g);
+  // this lane's 4 values: elements 4 cand .. 4 cand + 3 (two bf16 pairs), sign from "x < 0" (false for -0.0)
+  const uint32_t wa = cand == 0 ? ws[0] : cand == 1 ? ws[2] : cand == 2 ? ws[4] : ws[6];
+  const uint32_t wb = cand == 0 ? ws[1] : cand == 1 ? ws[3] : cand == 2 ? ws[5] : ws[7];
+  const float x0 = __uint_as_float(wa << 16), x1 = __uint_as_float(wa & 0xffff0000u);
+  const float x2 = __uint_as_float(wb << 16), x3 = __uint_as_float(wb & 0xffff0000u);
+  const uint32_t code = (mag_of(fabsf(x0), s) | (x0 < 0.0f ? 8u : 0u)) | ((mag_of(fabsf(x1), s) | (x1 < 0.0f ? 8u : 0u)) << 4) |
+                        ((mag_of(fabsf(x2), s) | (x2 < 0.0f ? 8u : 0u)) << 8) |
+                        ((mag_of(fabsf(x3), s) | (x3 < 0.0f ? 8u : 0u)) << 12);
   const long long page = slot / p.PS, pos = slot - page * p.PS;
-  uint8_t* dd = (side ? p.vd : p.kd) + page * p.dsp + pos * p.dst + h * p.dsh + blk * 8;
-  uint8_t* ds = (side ? p.vsf : p.ksf) + page * p.ssp + pos * p.sst + h * p.ssh + blk;
-  *reinterpret_cast<uint2*>(dd) = make_uint2(lo, hi);
-  *ds = (uint8_t)cb;
+  uint8_t* dd = (side ? p.vd : p.kd) + page * p.dsp + pos * p.dst + h * p.dsh + blk * 8 + 2 * cand;
+  *reinterpret_cast<uint16_t*>(dd) = (uint16_t)code;
+  if (cand == 0) (side ? p.vsf : p.ksf)[page * p.ssp + pos * p.sst + h * p.ssh + blk] = (uint8_t)cb;
 }
 
 static int g_last_cuda_error = 0;
@@ -180,16 +189,11 @@ extern "C" int hkv_write(const void* key, const void* val, int64_t ks0, int64_t 
   p.slots = (const long long*)slots;
   p.n_slots = n_slots;
   p.gk = gk; p.gv = gv; p.PS = PS; p.KVH = KVH;
-  const long long threads = n_slots * 2 * KVH * (D / 16);
+  const long long threads = n_slots * 2 * KVH * (D / 16) * 4;
   const long long blocks = (threads + 255) / 256;
   if (blocks > 0x7fffffffll) return HKV_ERR_RANGE;
   cudaStream_t st = (cudaStream_t)stream;
-  if (D == 128) {
-    if (search) write_kernel<128, 1><<<(unsigned)blocks, 256, 0, st>>>(p);
-    else write_kernel<128, 0><<<(unsigned)blocks, 256, 0, st>>>(p);
-  } else {
-    if (search) write_kernel<256, 1><<<(unsigned)blocks, 256, 0, st>>>(p);
-    else write_kernel<256, 0><<<(unsigned)blocks, 256, 0, st>>>(p);
-  }
-  return record_cuda(cudaGetLastError());
+  void (*k)(const WriteParams) = D == 128 ? (search ? write_kernel<128, 1> : write_kernel<128, 0>)
+                                          : (search ? write_kernel<256, 1> : write_kernel<256, 0>);
+  return record_cuda(launch_pdl(k, dim3((unsigned)blocks), dim3(256), 0, st, p));
 }

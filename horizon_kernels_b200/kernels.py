@@ -84,7 +84,7 @@ def write(key, value, flat, strides, PS, slot_mapping, gk, gv, search=True, sign
 
 def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_loc, bmm1_scale, bmm2_scale, gk, gv,
                   qlmax, out, workspace, splits=None, nst=None, ncw=None, min_chunk=None, tw=None, signs=None,
-                  k8=False):
+                  k8=False, _combine=True):
     """query (NT, HQ, D) bf16 contiguous; block_tables (B, MP) int32; seq_lens (B,) int32; query_start_loc (B + 1,)
     int32; out (>= NT, HQ, D) bf16, rows of requests without (or with more than qlmax) query tokens are left
     untouched; workspace from alloc_workspace. out = softmax(q k^T * bmm1_scale * gk) v * gv * bmm2_scale.
@@ -115,6 +115,8 @@ def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_
                           _ptr(seq_lens), _ptr(query_start_loc), B, KVH, G, D, int(qlmax), float(bmm1_scale),
                           float(bmm2_scale), _ptr(gk), _ptr(gv), _ptr(workspace), wsb, S, _ptr(out), s)
         _lib.check(rc, "hkv_decode")
+        if not _combine:                      # (benchmark only: time the decode kernel alone; `out` is incomplete)
+            return out
         rc = L.hkv_combine(_ptr(workspace), wsb, _ptr(query_start_loc), B, KVH, G, D, int(qlmax), float(bmm2_scale),
                            _ptr(out), s)
         _lib.check(rc, "hkv_combine")

@@ -1,0 +1,55 @@
+"""The plugin surface end to end on the GPU: HorizonFp4Impl.do_kv_cache_update + forward with metadata from
+HorizonFp4Builder, on a vLLM-shaped (blocks, 2*KVH, PS, slot) cache, against the CPU oracle
+(reference call path: nvidia-sm120/horizon_kvfp4/backend.py:389-436)."""
+import os
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+os.environ["HORIZON_KVFP4_STANDALONE"] = "1"
+import synth  # noqa: E402
+from cases import assert_close, bf16_tensor  # noqa: E402
+from horizon_kernels_b200 import backend as BE  # noqa: E402
+from horizon_kernels_b200 import layout as Lt  # noqa: E402
+from oracle import kvfp4 as O  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("KVH,G,D,PS", [(8, 4, 128, 16), (2, 8, 256, 16), (4, 2, 128, 64)])
+def test_update_then_forward_matches_oracle(KVH, G, D, PS):
+    lens = [300, 17, 2049, 64]
+    c = synth.paged_case(31 + D + PS, lens, KVH, G, D, PS, outliers=True)
+    dev = torch.device("cuda")
+    B, HQ = len(lens), KVH * G
+    kscale, vscale = 0.04, 0.009
+    layer = SimpleNamespace(_k_scale_float=kscale, _v_scale_float=vscale, layer_name="model.layers.3.self_attn.attn")
+    impl = BE.HorizonFp4Impl(HQ, D, D ** -0.5, num_kv_heads=KVH, kv_cache_dtype="nvfp4", max_num_seqs=16)
+    kv_cache = Lt.alloc_cache(c["NP"], PS, KVH, D, device=dev, fill=0x7F)
+    # prefill-style write of every cached token as flat (T, KVH * D) tensors, the shape vLLM passes
+    key = bf16_tensor(c["key"]).view(-1, KVH * D)
+    val = bf16_tensor(c["val"]).view(-1, KVH * D)
+    impl.do_kv_cache_update(layer, key, val, kv_cache, torch.from_numpy(c["slots"]).to(dev))
+    want = np.full(kv_cache.numel(), 0x7F, np.uint8)
+    lay = O.Layout.slots(PS, KVH, D)
+    gk = np.full(KVH, kscale, np.float32)
+    gv = np.full(KVH, vscale, np.float32)
+    O.write(c["key"], c["val"], want, lay, c["slots"], gk, gv, True)
+    assert np.array_equal(kv_cache.cpu().numpy().reshape(-1), want)
+
+    qsl = torch.from_numpy(c["qsl"])
+    cam = SimpleNamespace(num_reqs=B, num_actual_tokens=B, query_start_loc=qsl.to(dev), query_start_loc_cpu=qsl,
+                          seq_lens=torch.from_numpy(c["seq_lens"]).to(dev),
+                          block_table_tensor=torch.from_numpy(c["bt"]).to(dev),
+                          slot_mapping=torch.zeros(B, dtype=torch.int64, device=dev), seq_lens_cpu_upper_bound=None)
+    meta = BE.HorizonFp4Builder().build(0, cam)
+    query = bf16_tensor(c["q"]).view(B, HQ * D)
+    output = torch.full((B + 2, HQ * D), 5.0, dtype=torch.bfloat16, device=dev)      # padded, as under CUDA graphs
+    ret = impl.forward(layer, query, None, None, kv_cache, meta, output)
+    assert ret is output
+    ref, _ = O.attention(c["q"], want, lay, c["bt"], c["seq_lens"], c["qsl"], KVH, D ** -0.5, gk, gv, vscale)
+    scale = 1.0 / vscale                            # the output carries the extra v_scale factor: compare at unit scale
+    assert_close(output[:B].view(B, HQ, D).float() * scale, ref * scale)
+    assert (output[B:] == 5.0).all()
