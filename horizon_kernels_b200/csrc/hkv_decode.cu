@@ -808,3 +808,52 @@ extern "C" int hkv_workspace_status(void* workspace, int* status, void* stream) 
   if ((e = cudaMemsetAsync(workspace, 0, sizeof(int), st)) != cudaSuccess) return record_cuda(e);
   return record_cuda(cudaStreamSynchronize(st));
 }
+
+// ------------------------------------------------------------------------------------------ decode without a workspace
+namespace hkv {
+// Scratch of the workspace-free entry point: partition descriptors, log2-sum-exp values and fp32 partials of one
+// decode call. 5 MiB hold 444 partitions at head_dim 128 (3.7 MB) and 296 at head_dim 256 (4.9 MB), which is what a
+// 148-SM device uses. Every GPU that loads this library carries the array until the process exits.
+constexpr size_t kNoAllocScratchBytes = 5u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+// device address of the array per device ordinal; the symbol's name above is only a host-side handle
+static void* g_noalloc_ptr[64] = {};
+}  // namespace hkv
+
+extern "C" int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
+                                  const int64_t strides[6], int PS, const int32_t* block_tables, int MP,
+                                  const int32_t* seq_lens, const int32_t* query_start_loc, int B, int KVH, int G, int D,
+                                  int qlmax, float sm_scale, float v_scale, const float* gk, const float* gv, int splits,
+                                  void* out, void* stream) {
+  using namespace hkv;
+  if (B < 0 || MP < 0 || splits < 0) return HKV_ERR_RANGE;
+  if (B == 0) return HKV_OK;
+  if (D != 128 && D != 256) return HKV_ERR_UNSUPPORTED;
+  if (KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > RPAD) return HKV_ERR_UNSUPPORTED;
+  if (splits > 64) return HKV_ERR_SPLITS;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return record_cuda(e);
+  if (dev < 0 || dev >= 64) return HKV_ERR_RANGE;
+  if (g_noalloc_ptr[dev] == nullptr) {              // set-up, once per device, with that device current
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess) return record_cuda(e);
+    if (ptr == nullptr) return HKV_ERR_CUDA;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  DeviceInfo* di;
+  const int rc0 = device_info(&di);
+  if (rc0 != HKV_OK) return rc0;
+  // the scratch a call needs grows with the number of stream partitions, which is bounded by the device's resident
+  // CTAs and by B * KVH * splits
+  long long n_parts = (long long)di->sms * std::max(di->ctas_per_sm[D == 256][0], di->ctas_per_sm[D == 256][1]);
+  if (splits > 0) n_parts = std::min<long long>(n_parts, (long long)B * KVH * splits);
+  if (n_parts < 1) n_parts = 1;
+  if (WorkspaceLayout((int)n_parts, RPAD, D).total > kNoAllocScratchBytes) return HKV_ERR_NOALLOC_LIMIT;
+  void* ws = g_noalloc_ptr[dev];
+  const int rc = hkv_decode(q, kd, ksf, vd, vsf, strides, PS, block_tables, MP, seq_lens, query_start_loc, B, KVH, G, D,
+                            qlmax, sm_scale, v_scale, gk, gv, ws, kNoAllocScratchBytes, splits, out, stream);
+  if (rc != HKV_OK) return rc;
+  return hkv_combine(ws, kNoAllocScratchBytes, query_start_loc, B, KVH, G, D, qlmax, v_scale, out, stream);
+}

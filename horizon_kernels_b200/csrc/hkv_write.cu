@@ -152,6 +152,9 @@ extern "C" const char* hkv_error_string(int code) {
     case HKV_ERR_RANGE: return "a size is negative or too large";
     case HKV_ERR_CUDA: return "a CUDA runtime call failed";
     case HKV_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel ran out";
+    case HKV_ERR_NOALLOC_LIMIT:
+      return "the call needs more scratch than the built-in 5 MiB of hkv_decode_noalloc: pass a smaller `splits` or use "
+             "hkv_decode with a workspace";
     default: return "unknown error code";
   }
 }

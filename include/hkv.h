@@ -35,6 +35,7 @@ extern "C" {
 #define HKV_ERR_RANGE (-6)        /* a size is negative or too large */
 #define HKV_ERR_CUDA (-7)         /* a CUDA runtime call failed; hkv_last_cuda_error() has the code */
 #define HKV_ERR_DEVICE_WAIT (-8)  /* a bounded wait inside a kernel ran out (read back by hkv_workspace_status) */
+#define HKV_ERR_NOALLOC_LIMIT (-9) /* hkv_decode_noalloc: the call needs more than the built-in scratch */
 
 /* library version (major * 10000 + minor * 100 + patch) and a text for an error code */
 int hkv_version(void);
@@ -90,6 +91,34 @@ int hkv_decode(const void* q, const void* kd, const void* ksf, const void* vd, c
  */
 int hkv_combine(const void* workspace, size_t workspace_bytes, const int32_t* query_start_loc, int B, int KVH, int G,
                 int D, int qlmax, float v_scale, void* out, void* stream);
+
+/*
+ * Decode + combine for callers that cannot allocate device memory. This entry point has no counterpart in the
+ * reference, whose backend always allocates its workspace with torch.
+ *
+ * Who needs it: an inference server usually hands nearly all device memory to one pool at start-up, and a component
+ * that is loaded afterwards (a plugin, a sidecar runtime written in another language, code that runs while another
+ * library is capturing a CUDA graph) finds cudaMalloc either failing for lack of memory or forbidden outright. Such a
+ * caller passes the same inputs and the output buffer as for hkv_decode + hkv_combine, but no workspace: the scratch is
+ * a 5 MiB array built into the library (HKV_NOALLOC_SCRATCH_BYTES), resident on every GPU that loads it.
+ *
+ * Limits and rules:
+ *   - The scratch holds the partials of at most 444 partitions at head_dim 128 or 296 at head_dim 256 (what a 148-SM
+ *     GPU uses). A call that would need more returns HKV_ERR_NOALLOC_LIMIT and launches nothing; a smaller `splits`
+ *     (partitions <= B * KVH * splits) brings it under the limit.
+ *   - The first call on a device looks up the array's device address and configures the kernels. Make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one array. Two calls whose kernels can overlap on the GPU (different streams
+ *     without an ordering between them) race on it; order them on one stream or with events. Nothing in the array has
+ *     to be cleared between calls: every call rewrites the part it reads.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ * Arguments as for hkv_decode (without workspace, workspace_bytes); `out` is complete when the call's kernels finish.
+ */
+#define HKV_NOALLOC_SCRATCH_BYTES (5u << 20)
+int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
+                       const int64_t strides[6], int PS, const int32_t* block_tables, int MP, const int32_t* seq_lens,
+                       const int32_t* query_start_loc, int B, int KVH, int G, int D, int qlmax, float sm_scale,
+                       float v_scale, const float* gk, const float* gv, int splits, void* out, void* stream);
 
 /*
  * Copies the workspace's device status word to *status (HKV_OK or HKV_ERR_DEVICE_WAIT) and clears it. Synchronises the
