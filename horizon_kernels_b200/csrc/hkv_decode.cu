@@ -63,8 +63,12 @@ struct Geo {
   static constexpr int SD = D / 2, SS = D / 16, SLOT = SD + SS;
   static constexpr int UB = D == 128 ? 2 : 1;          // 16-token blocks per unit
   static constexpr int UT = 16 * UB, LOG_UT = UB == 2 ? 5 : 4;
-  static constexpr int NS = D == 128 ? 3 : 4;          // stages per warp
-  static constexpr int MINB = D == 128 ? 3 : 2;        // CTAs per SM the register budget is sized for
+#ifndef HKV_NS128
+#define HKV_NS128 3
+#define HKV_MINB128 3
+#endif
+  static constexpr int NS = D == 128 ? HKV_NS128 : 4;  // stages per warp
+  static constexpr int MINB = D == 128 ? HKV_MINB128 : 2;   // CTAs per SM the register budget is sized for
   static constexpr int TILE = UT * SLOT;               // bytes of one (head, side) tile of a unit
   static constexpr int STAGE = 2 * TILE;
   static constexpr int ROW = LAYOUT == 0 ? SLOT : SD;  // byte stride between code rows in shared memory
@@ -635,23 +639,37 @@ __global__ void __launch_bounds__(128) combine_kernel(const uint8_t* ws, const i
   ql = (ql < 0 || ql > qlmax) ? 0 : ql;
   const int R = G * ql;
   const float ninf = -__int_as_float(0x7f800000);
+  const int first = d.first_part, first_slot = d.first_slot;
   for (int idx = tid; idx < R * (D / 2); idx += 128) {
     const int row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
-    float mx = ninf;
-    for (int pc = d.first_part; pc <= part; ++pc) {
-      const int slot = pc * 2 + (pc == d.first_part ? d.first_slot : 0);
-      mx = fmaxf(mx, lse_ws[slot * RPAD + row]);
-    }
-    float tot = 0.0f, n0 = 0.0f, n1 = 0.0f;
-    for (int pc = d.first_part; pc <= part; ++pc) {
-      const int slot = pc * 2 + (pc == d.first_part ? d.first_slot : 0);
-      const float ls = lse_ws[slot * RPAD + row];
-      if (ls == ninf) continue;                      // an empty piece: its partial is never read
-      const float wgt = exp2f(ls - mx);
-      const float2 v = *reinterpret_cast<const float2*>(opart_ws + ((size_t)slot * RPAD + row) * D + ch);
-      tot += wgt;
-      n0 += v.x * wgt;
-      n1 += v.y * wgt;
+    // pieces are merged four at a time: the loads of a group are independent of each other, and a running maximum
+    // carries the log-sum-exp weights from group to group (fixed order, so the result is deterministic)
+    float mx = ninf, tot = 0.0f, n0 = 0.0f, n1 = 0.0f;
+    for (int pc0 = first; pc0 <= part; pc0 += 4) {
+      float ls[4];
+      float2 v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int pc = pc0 + i;
+        const int slot = pc * 2 + (pc == first ? first_slot : 0);
+        const bool on = pc <= part;
+        ls[i] = on ? lse_ws[slot * RPAD + row] : ninf;
+        v[i] = on ? *reinterpret_cast<const float2*>(opart_ws + ((size_t)slot * RPAD + row) * D + ch) : make_float2(0.f, 0.f);
+      }
+      const float gm = fmaxf(fmaxf(ls[0], ls[1]), fmaxf(ls[2], ls[3]));
+      if (gm == ninf) continue;                      // only empty pieces in this group
+      const float nm = fmaxf(mx, gm);
+      const float keep = mx == ninf ? 0.0f : exp2f(mx - nm);
+      tot *= keep; n0 *= keep; n1 *= keep;
+      mx = nm;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (ls[i] == ninf) continue;                 // an empty piece: its partial is garbage and must not be used
+        const float wgt = exp2f(ls[i] - nm);
+        tot += wgt;
+        n0 += v[i].x * wgt;
+        n1 += v[i].y * wgt;
+      }
     }
     const float inv = tot > 0.0f ? v_scale / tot : 0.0f;
     const int t = row / G, gq = row - t * G;
