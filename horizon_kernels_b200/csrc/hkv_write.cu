@@ -10,6 +10,7 @@
 // through an explicit intrinsic (__fdiv_rn, __fmul_rn, __fsub_rn, __fadd_rn): no contraction into FMA, no fast-math.
 // The squared error is summed sequentially over i = 0..15 and a later candidate wins only on a strict "<".
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
 #include "hkv_common.cuh"
@@ -64,27 +65,69 @@ __device__ __forceinline__ float block_sse(const float (&ax)[16], float s) {
   return acc;
 }
 
+// ---- division-free fast path -------------------------------------------------------------------------------------
+// The reference rounds y = RN(ax / s) onto the E2M1 grid. Here y is approximated by ax * RN(1 / s) (relative error
+// below 2^-22) and the hardware conversion cvt.rn.satfinite.e2m1x2.f32 (identical to the reference's threshold chain
+// for every non-negative fp32 input) is applied to y * (1 + 2^-20) and y * (1 - 2^-20) at once. The conversion is
+// monotone and RN(ax / s) lies between the two arguments, so equal codes prove the code of the exact quotient; a
+// block with any unequal pair, or a scale outside [2^-96, 2^96], is redone with IEEE divisions. The error terms
+// (code * s - ax)^2 are still single IEEE operations in the reference's order.
+__device__ __forceinline__ unsigned e2m1_pair(float hi, float lo) {      // code(hi) in bits 7:4, code(lo) in bits 3:0
+  unsigned short r;
+  asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; mov.b16 %0, {t, 0}; }" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float e2m1_pair_value(unsigned b) {           // value of the code in bits 3:0
+  unsigned h2;
+  asm("{ .reg .b8 t, z; mov.b16 {t, z}, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h2) : "h"((unsigned short)b));
+  return __half2float(__ushort_as_half((unsigned short)(h2 & 0xffffu)));
+}
+constexpr float kUp = 1.0f + 9.5367431640625e-07f, kDown = 1.0f - 9.5367431640625e-07f;   // 1 +- 2^-20
+__device__ __forceinline__ bool fast_scale_ok(float s) { return s >= 1.2621774e-29f && s <= 7.9228163e28f; }
+
+// squared error of the block under scale s with reciprocal r; `risk` collects code disagreements (bits 3:0)
+__device__ __forceinline__ float block_sse_fast(const float (&ax)[16], float s, float r, unsigned& risk) {
+  float acc = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float y = ax[i] * r;
+    const unsigned b = e2m1_pair(y * kUp, y * kDown);
+    risk |= b ^ (b >> 4);
+    const float d = __fsub_rn(__fmul_rn(e2m1_pair_value(b), s), ax[i]);
+    const float sq = __fmul_rn(d, d);
+    acc = i == 0 ? sq : __fadd_rn(acc, sq);
+  }
+  return acc;
+}
+
 // Four lanes share one block of 16 values: every lane reads the whole block (the four identical 16-byte requests of
 // a quad are served by one access), lane k of the quad scores scale candidate k, the quad agrees on the winner with
 // shuffles in candidate order (strict "<", so the earliest candidate wins a tie, as in the reference), and every lane
-// encodes 4 of the 16 values. One (token, kv head, side) row of D values is 4 * D / 16 consecutive threads.
+// encodes 4 of the 16 values. One CTA of 256 threads (64 quads) handles one token: 2 * KVH * D / 16 blocks.
 template <int D, int SEARCH>
 __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   constexpr int NB = D / 16;                      // blocks per row
   pdl_wait();                                     // inputs and the cache may come from the preceding launch
   pdl_launch_dependents();
-  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const int cand = (int)(gid & 3);
-  const long long bid = gid >> 2;
-  const int per_tok = 2 * p.KVH * NB;
-  const long long t = bid / per_tok;
-  if (t >= p.n_slots) return;                     // uniform per quad: a quad never straddles two tokens
-  const int rem = (int)(bid - t * per_tok);
-  const int side = rem / (p.KVH * NB);
-  const int hb = rem - side * (p.KVH * NB);
-  const int h = hb / NB, blk = hb - h * NB;
+  // one CTA per token; its 2 * KVH * NB blocks are spread over the CTA's quads (all index math in 32 bits)
+  const long long t = blockIdx.x;
   const long long slot = p.slots[t];
-  if (slot < 0) return;
+  if (slot < 0) return;                           // uniform per CTA
+  long long page, pos;
+  if ((p.PS & (p.PS - 1)) == 0) {
+    const int sh = 31 - __clz(p.PS);
+    page = slot >> sh;
+    pos = slot & (p.PS - 1);
+  } else {
+    page = slot / p.PS;
+    pos = slot - page * p.PS;
+  }
+  const int cand = threadIdx.x & 3;
+  const int n_blocks = 2 * p.KVH * NB;
+  for (int bid = threadIdx.x >> 2; bid < n_blocks; bid += 64) {   // 64 quads per CTA; n_blocks is a multiple of 16
+  const int side = bid >= p.KVH * NB;
+  const int hb = side ? bid - p.KVH * NB : bid;
+  const int h = hb / NB, blk = hb - h * NB;
 
   const __nv_bfloat16* src = side ? p.val + t * p.vs0 + h * p.vs1 : p.key + t * p.ks0 + h * p.ks1;
   const uint4 w0 = *reinterpret_cast<const uint4*>(src + blk * 16);
@@ -104,7 +147,12 @@ __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   if (SEARCH) {
     const int cc = cand == 0 ? c0 : cand == 1 ? min(c0 + 1, 126) : cand == 2 ? max(c0 - 1, 0)
                  : (int)e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 4.0f)));
-    const float err = block_sse(ax, __fmul_rn(e4m3_dec((unsigned)cc), g));
+    const float sc = __fmul_rn(e4m3_dec((unsigned)cc), g);
+    float err;
+    unsigned risk = fast_scale_ok(sc) ? 0u : 15u;
+    if (risk == 0u) err = block_sse_fast(ax, sc, __frcp_rn(sc), risk);
+    if (risk & 15u) err = block_sse(ax, sc);          // rare: a quotient too close to a rounding boundary, or a
+                                                      // zero / extreme scale
     const int lane0 = (threadIdx.x & 31) & ~3;
     float best = __shfl_sync(0xffffffffu, err, lane0);
     cb = __shfl_sync(0xffffffffu, cc, lane0);
@@ -124,13 +172,25 @@ __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   const uint32_t wb = cand == 0 ? ws[1] : cand == 1 ? ws[3] : cand == 2 ? ws[5] : ws[7];
   const float x0 = __uint_as_float(wa << 16), x1 = __uint_as_float(wa & 0xffff0000u);
   const float x2 = __uint_as_float(wb << 16), x3 = __uint_as_float(wb & 0xffff0000u);
-  const uint32_t code = (mag_of(fabsf(x0), s) | (x0 < 0.0f ? 8u : 0u)) | ((mag_of(fabsf(x1), s) | (x1 < 0.0f ? 8u : 0u)) << 4) |
-                        ((mag_of(fabsf(x2), s) | (x2 < 0.0f ? 8u : 0u)) << 8) |
-                        ((mag_of(fabsf(x3), s) | (x3 < 0.0f ? 8u : 0u)) << 12);
-  const long long page = slot / p.PS, pos = slot - page * p.PS;
+  unsigned m0, m1, m2, m3;
+  unsigned risk = fast_scale_ok(s) ? 0u : 15u;
+  if (risk == 0u) {
+    const float r = __frcp_rn(s);
+    const float y0 = fabsf(x0) * r, y1 = fabsf(x1) * r, y2 = fabsf(x2) * r, y3 = fabsf(x3) * r;
+    const unsigned b0 = e2m1_pair(y0 * kUp, y0 * kDown), b1 = e2m1_pair(y1 * kUp, y1 * kDown);
+    const unsigned b2 = e2m1_pair(y2 * kUp, y2 * kDown), b3 = e2m1_pair(y3 * kUp, y3 * kDown);
+    risk = (b0 ^ (b0 >> 4)) | (b1 ^ (b1 >> 4)) | (b2 ^ (b2 >> 4)) | (b3 ^ (b3 >> 4));
+    m0 = b0 & 7u; m1 = b1 & 7u; m2 = b2 & 7u; m3 = b3 & 7u;
+  }
+  if (risk & 15u) {
+    m0 = mag_of(fabsf(x0), s); m1 = mag_of(fabsf(x1), s); m2 = mag_of(fabsf(x2), s); m3 = mag_of(fabsf(x3), s);
+  }
+  const uint32_t code = (m0 | (x0 < 0.0f ? 8u : 0u)) | ((m1 | (x1 < 0.0f ? 8u : 0u)) << 4) |
+                        ((m2 | (x2 < 0.0f ? 8u : 0u)) << 8) | ((m3 | (x3 < 0.0f ? 8u : 0u)) << 12);
   uint8_t* dd = (side ? p.vd : p.kd) + page * p.dsp + pos * p.dst + h * p.dsh + blk * 8 + 2 * cand;
   *reinterpret_cast<uint16_t*>(dd) = (uint16_t)code;
   if (cand == 0) (side ? p.vsf : p.ksf)[page * p.ssp + pos * p.sst + h * p.ssh + blk] = (uint8_t)cb;
+  }
 }
 
 static int g_last_cuda_error = 0;
@@ -192,8 +252,7 @@ extern "C" int hkv_write(const void* key, const void* val, int64_t ks0, int64_t 
   p.slots = (const long long*)slots;
   p.n_slots = n_slots;
   p.gk = gk; p.gv = gv; p.PS = PS; p.KVH = KVH;
-  const long long threads = n_slots * 2 * KVH * (D / 16) * 4;
-  const long long blocks = (threads + 255) / 256;
+  const long long blocks = n_slots;                 // one CTA per token
   if (blocks > 0x7fffffffll) return HKV_ERR_RANGE;
   cudaStream_t st = (cudaStream_t)stream;
   void (*k)(const WriteParams) = D == 128 ? (search ? write_kernel<128, 1> : write_kernel<128, 0>)

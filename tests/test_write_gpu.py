@@ -46,6 +46,12 @@ def kv_tokens(seed, NT, KVH, D, kind):
         if NT > 3: v[3] *= 1e30
         if NT > 4: k[4, :, :16] = 300.0
         if NT > 5: v[5, :, ::3] = -0.0
+        ties = np.tile(np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0,
+                                 -6.0]), D // 16)          # quotients exactly on the rounding boundaries
+        if NT > 6: k[6] = ties
+        if NT > 7: v[7] = ties * 0.125
+        if NT > 8: k[8] = ties * 3.0
+        if NT > 9: v[9] = ties * (1.0 + 2.0 ** -7)
     return synth.to_bf16_bits(k), synth.to_bf16_bits(v)
 
 
