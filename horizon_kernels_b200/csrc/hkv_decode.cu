@@ -627,11 +627,12 @@ __global__ void __launch_bounds__(128) combine_kernel(const uint8_t* ws, const i
   const int part = blockIdx.x, tid = threadIdx.x;
   pdl_wait();                                     // the workspace is written by the preceding decode launch
   pdl_launch_dependents();
+  // the descriptor table sits at a fixed offset, so its load does not wait for the header's
+  const PartDesc d = reinterpret_cast<const PartDesc*>(ws + align_up(sizeof(Header), 256))[part < 0 ? 0 : part];
   const int n_parts = reinterpret_cast<const Header*>(ws)->n_parts;
   if (part >= n_parts) return;
-  const WorkspaceLayout wl(n_parts, RPAD, D);
-  const PartDesc d = reinterpret_cast<const PartDesc*>(ws + wl.desc_off)[part];
   if (d.b < 0 || d.blk_begin == 0 || d.blk_end != d.units) return;
+  const WorkspaceLayout wl(n_parts, RPAD, D);
   const float* lse_ws = reinterpret_cast<const float*>(ws + wl.lse_off);
   const float* opart_ws = reinterpret_cast<const float*>(ws + wl.opart_off);
   const int q0 = qsl[d.b];
@@ -640,30 +641,32 @@ __global__ void __launch_bounds__(128) combine_kernel(const uint8_t* ws, const i
   const int R = G * ql;
   const float ninf = -__int_as_float(0x7f800000);
   const int first = d.first_part, first_slot = d.first_slot;
-  for (int idx = tid; idx < R * (D / 2); idx += 128) {
+  constexpr int GRP = 8;                            // pieces merged per round: their loads are independent
+  for (int idx = tid; idx < G * qlmax * (D / 2); idx += 128) {
     const int row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
-    // pieces are merged four at a time: the loads of a group are independent of each other, and a running maximum
-    // carries the log-sum-exp weights from group to group (fixed order, so the result is deterministic)
+    // a running maximum carries the log-sum-exp weights from round to round (fixed order => deterministic)
     float mx = ninf, tot = 0.0f, n0 = 0.0f, n1 = 0.0f;
-    for (int pc0 = first; pc0 <= part; pc0 += 4) {
-      float ls[4];
-      float2 v[4];
+    for (int pc0 = first; pc0 <= part; pc0 += GRP) {
+      float ls[GRP];
+      float2 v[GRP];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < GRP; ++i) {
         const int pc = pc0 + i;
         const int slot = pc * 2 + (pc == first ? first_slot : 0);
         const bool on = pc <= part;
         ls[i] = on ? lse_ws[slot * RPAD + row] : ninf;
         v[i] = on ? *reinterpret_cast<const float2*>(opart_ws + ((size_t)slot * RPAD + row) * D + ch) : make_float2(0.f, 0.f);
       }
-      const float gm = fmaxf(fmaxf(ls[0], ls[1]), fmaxf(ls[2], ls[3]));
-      if (gm == ninf) continue;                      // only empty pieces in this group
+      float gm = ls[0];
+#pragma unroll
+      for (int i = 1; i < GRP; ++i) gm = fmaxf(gm, ls[i]);
+      if (gm == ninf) continue;                      // only empty pieces in this round
       const float nm = fmaxf(mx, gm);
       const float keep = mx == ninf ? 0.0f : exp2f(mx - nm);
       tot *= keep; n0 *= keep; n1 *= keep;
       mx = nm;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < GRP; ++i) {
         if (ls[i] == ninf) continue;                 // an empty piece: its partial is garbage and must not be used
         const float wgt = exp2f(ls[i] - nm);
         tot += wgt;
@@ -671,10 +674,12 @@ __global__ void __launch_bounds__(128) combine_kernel(const uint8_t* ws, const i
         n1 += v[i].y * wgt;
       }
     }
-    const float inv = tot > 0.0f ? v_scale / tot : 0.0f;
-    const int t = row / G, gq = row - t * G;
-    __nv_bfloat16* dst = out + ((long long)(q0 + t) * (KVH * G) + d.h * G + gq) * D + ch;
-    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(n0 * inv, n1 * inv);
+    if (row < R) {
+      const float inv = tot > 0.0f ? v_scale / tot : 0.0f;
+      const int t = row / G, gq = row - t * G;
+      __nv_bfloat16* dst = out + ((long long)(q0 + t) * (KVH * G) + d.h * G + gq) * D + ch;
+      *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(n0 * inv, n1 * inv);
+    }
   }
 }
 

@@ -10,6 +10,8 @@
 // through an explicit intrinsic (__fdiv_rn, __fmul_rn, __fsub_rn, __fadd_rn): no contraction into FMA, no fast-math.
 // The squared error is summed sequentially over i = 0..15 and a later candidate wins only on a strict "<".
 #include <cuda_bf16.h>
+
+#include <algorithm>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
@@ -103,9 +105,9 @@ __device__ __forceinline__ float block_sse_fast(const float (&ax)[16], float s, 
 // Four lanes share one block of 16 values: every lane reads the whole block (the four identical 16-byte requests of
 // a quad are served by one access), lane k of the quad scores scale candidate k, the quad agrees on the winner with
 // shuffles in candidate order (strict "<", so the earliest candidate wins a tie, as in the reference), and every lane
-// encodes 4 of the 16 values. One CTA of 256 threads (64 quads) handles one token: 2 * KVH * D / 16 blocks.
+// encodes 4 of the 16 values. One CTA handles one token: 2 * KVH * D / 16 blocks spread over its quads.
 template <int D, int SEARCH>
-__global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
+__global__ void __launch_bounds__(1024) write_kernel(const WriteParams p) {
   constexpr int NB = D / 16;                      // blocks per row
   pdl_wait();                                     // inputs and the cache may come from the preceding launch
   pdl_launch_dependents();
@@ -124,7 +126,7 @@ __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   }
   const int cand = threadIdx.x & 3;
   const int n_blocks = 2 * p.KVH * NB;
-  for (int bid = threadIdx.x >> 2; bid < n_blocks; bid += 64) {   // 64 quads per CTA; n_blocks is a multiple of 16
+  for (int bid = threadIdx.x >> 2; bid < n_blocks; bid += blockDim.x >> 2) {   // n_blocks is a multiple of 16
   const int side = bid >= p.KVH * NB;
   const int hb = side ? bid - p.KVH * NB : bid;
   const int h = hb / NB, blk = hb - h * NB;
@@ -257,5 +259,9 @@ extern "C" int hkv_write(const void* key, const void* val, int64_t ks0, int64_t 
   cudaStream_t st = (cudaStream_t)stream;
   void (*k)(const WriteParams) = D == 128 ? (search ? write_kernel<128, 1> : write_kernel<128, 0>)
                                           : (search ? write_kernel<256, 1> : write_kernel<256, 0>);
-  return record_cuda(launch_pdl(k, dim3((unsigned)blocks), dim3(256), 0, st, p));
+  // few tokens (decode appends): one quad per block so that a token's blocks are quantised side by side; many tokens
+  // (prefill): 256 threads per CTA loop over the token's blocks
+  int threads = 256;
+  if (n_slots <= 4096) threads = std::min(1024, std::max(128, 2 * KVH * (D / 16) * 4));
+  return record_cuda(launch_pdl(k, dim3((unsigned)blocks), dim3(threads), 0, st, p));
 }
