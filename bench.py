@@ -187,6 +187,7 @@ def run_reference(args, cfg):
     import synth
     KVH, D, PS, HQ = cfg["KVH"], cfg["D"], cfg["PS"], cfg["HQ"]
     lens_all = draw_lens(cfg, args.seed * 131)
+    O.set_num_threads(len(os.sched_getaffinity(0)))        # every host core (torchrun would pin OpenMP to one thread)
     cores = O.num_threads()
     # sample size: requests whose contexts add up to about 40k tokens (a step of a few seconds on ~8 cores)
     rows, tok = [], 0
@@ -450,8 +451,9 @@ def main():
         host_pool = pool.cpu().numpy().reshape(-1)
         bt_np, q_bits = bt.bt.cpu().numpy(), bt.q.cpu().view(torch.int16).numpy().view(np.uint16)
         gk_np, gv_np = gk.cpu().numpy(), gv.cpu().numpy()
+        O_threads = len(os.sched_getaffinity(0))
         order = sorted(range(B), key=lambda r: bt.lens[r])
-        _, t1, cores = oracle_sample(cfg, host_pool, bt_np, bt.lens, q_bits, gk_np, gv_np, order[:1])
+        _, t1, cores = oracle_sample(cfg, host_pool, bt_np, bt.lens, q_bits, gk_np, gv_np, order[:1], O_threads)
         rate = bt.lens[order[0]] / max(t1, 1e-6)                         # cached tokens per second, first estimate
         rows, tok = [], 0
         for r in range(B):
@@ -459,7 +461,7 @@ def main():
                 break
             rows.append(r)
             tok += bt.lens[r]
-        ref, secs, cores = oracle_sample(cfg, host_pool, bt_np, bt.lens, q_bits, gk_np, gv_np, rows)
+        ref, secs, cores = oracle_sample(cfg, host_pool, bt_np, bt.lens, q_bits, gk_np, gv_np, rows, O_threads)
         got = bt.out[rows].float().cpu().numpy().astype(np.float64)
         d = np.abs(got - ref)
         line["cpu_baseline"] = {"value": len(rows) / secs, "unit": "tokens/s", "cores": cores, "kind": "port",
