@@ -86,6 +86,25 @@ def test_decode_matches_oracle(lens, KVH, G, D, PS, kind):
         assert_close(o3, ref, f"{lens} splits {splits}")
 
 
+def test_large_ragged_batch():
+    """300 requests, lengths log-uniform in [1, 3000] with some empty contexts and some padding requests (0 query
+    tokens): the per-CTA prefix scan spans several 32-request groups and most partitions hold many short sequences"""
+    B = 300
+    u = synth.uniform(555, B)
+    lens = [int(np.exp(x * np.log(3000.0))) for x in u]
+    for i in range(0, B, 37):
+        lens[i] = 0
+    qls = [0 if i % 41 == 5 else 1 for i in range(B)]
+    for D, KVH, G in ((128, 8, 4), (256, 2, 8)):
+        c = build_decode_case(2500 + D, lens, KVH, G, D, 16, ql_list=qls)
+        ref = oracle_decode(c)
+        out, ws = gpu_decode(c)
+        assert K.workspace_status(ws) == 0
+        assert_close(out, ref, f"D{D}")
+        out2, _ = gpu_decode(c, ws=ws)
+        assert torch.equal(out, out2)
+
+
 def test_rows_without_query_tokens_are_untouched():
     """a graph-padding request (0 query tokens) and a prefill row (more than qlmax tokens) are skipped"""
     lens = [40, 300, 64, 90]
