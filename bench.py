@@ -35,6 +35,10 @@ WORKLOADS = {
     "c0": dict(B=4, HQ=32, KVH=8, D=128, PS=16, pool=1024, law=("const", 2048)),
     "c1": dict(B=64, HQ=32, KVH=8, D=128, PS=16, pool=37500, law=("uniform", 1024, 8192)),
     "c2": dict(B=8, HQ=64, KVH=8, D=128, PS=16, pool=8 * 8192 * 2 + 16, law=("const", 131072)),
+    # hybrid batch sharded by request over the GPUs (strong scaling): one batch (6.9 GB of cache reads at N = 1) in a
+    # page pool of up to 150 GB per GPU
+    "c4": dict(B=2048, HQ=16, KVH=2, D=256, PS=16, pool=int(150e9) // (2 * 2 * 16 * 144), law=("loguniform", 128, 32768),
+               sharded=True, n_batches=1),
 }
 METRIC = "decode_attn_tokens_per_s"
 
@@ -45,6 +49,8 @@ def draw_lens(cfg, seed):
     law = cfg["law"]
     if law[0] == "const":
         return [law[1]] * cfg["B"]
+    if law[0] == "loguniform":
+        return [int(round(math.exp(x))) for x in rng.uniform(math.log(law[1]), math.log(law[2]), cfg["B"])]
     return [int(x) for x in rng.integers(law[1], law[2] + 1, cfg["B"])]
 
 
@@ -96,15 +102,20 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------------- workload
-def build_batches(cfg, seed, device, n_batches=2):
-    """n_batches decode batches over disjoint pages of one cache pool, written by the CUDA write kernel"""
+def build_batches(cfg, seed, device, n_batches=2, rows=None, lens_seed=None):
+    """n_batches decode batches over disjoint pages of one cache pool, written by the CUDA write kernel. `rows` keeps
+    only these requests of every batch (the shard of one rank); lens_seed fixes the length draw across ranks."""
     import torch
     from horizon_kernels_b200 import kernels as K
     from horizon_kernels_b200 import layout as Lt
-    B, HQ, KVH, D, PS = cfg["B"], cfg["HQ"], cfg["KVH"], cfg["D"], cfg["PS"]
+    HQ, KVH, D, PS = cfg["HQ"], cfg["KVH"], cfg["D"], cfg["PS"]
+    B = cfg["B"] if rows is None else len(rows)
     g = torch.Generator(device=device).manual_seed(seed)
-    pool = torch.empty((cfg["pool"], 2 * KVH, PS, Lt.slot_bytes(D)), dtype=torch.uint8, device=device)
-    perm = torch.randperm(cfg["pool"], generator=g, device=device).to(torch.int32)
+    page_b = 2 * KVH * PS * Lt.slot_bytes(D)
+    free_b, _ = torch.cuda.mem_get_info(device)
+    n_pool = min(cfg["pool"], int((free_b - (24 << 30)) // page_b)) if cfg.get("sharded") else cfg["pool"]
+    pool = torch.empty((n_pool, 2 * KVH, PS, Lt.slot_bytes(D)), dtype=torch.uint8, device=device)
+    perm = torch.randperm(n_pool, generator=g, device=device).to(torch.int32)
     ch = torch.tensor([3, D // 4 + 3, D // 2 + 3, 3 * D // 4 + 3], device=device)
     # global scales amax / (6 * 448): K ~ N(0,1) with x20 outlier channels, V ~ N(0,1); fixed from the distribution's
     # range so that every batch and rank shares them (5.5 sigma)
@@ -113,10 +124,12 @@ def build_batches(cfg, seed, device, n_batches=2):
     flat, strides = Lt.flat_views(*Lt.slot_views(pool, KVH, D))
     batches, used = [], 0
     for bi in range(n_batches):
-        lens = draw_lens(cfg, seed * 131 + bi)
+        lens = draw_lens(cfg, (seed if lens_seed is None else lens_seed) * 131 + bi)
+        if rows is not None:
+            lens = [lens[r] for r in rows]
         pages = [(L + PS - 1) // PS for L in lens]
         tot = sum(pages)
-        if used + tot > cfg["pool"]:
+        if used + tot > n_pool:
             raise RuntimeError("page pool too small for the batches")
         mine = perm[used:used + tot]
         used += tot
@@ -267,10 +280,19 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     B, HQ, KVH, D, PS = cfg["B"], cfg["HQ"], cfg["KVH"], cfg["D"], cfg["PS"]
-    pool, (flat, strides), gk, gv, batches = build_batches(cfg, args.seed + 1000 * rank, device)
+    NBT = cfg.get("n_batches", 2)
+    if cfg.get("sharded"):
+        # one batch for the whole job, partitioned by cached tokens; every rank builds only its own requests
+        from horizon_kernels_b200.sharding import partition_requests
+        lens_all = draw_lens(cfg, args.seed * 131)
+        rows = partition_requests(lens_all, world)[rank]
+        pool, (flat, strides), gk, gv, batches = build_batches(cfg, args.seed + 1000 * rank, device, NBT, rows, args.seed)
+        B = len(rows)
+    else:
+        pool, (flat, strides), gk, gv, batches = build_batches(cfg, args.seed + 1000 * rank, device, NBT)
     for bt in batches:
         bt.qsl_cpu = bt.qsl.cpu()
-    impl = BE.HorizonFp4Impl(HQ, D, float(D) ** -0.5, num_kv_heads=KVH, kv_cache_dtype="nvfp4", max_num_seqs=B)
+    impl = BE.HorizonFp4Impl(HQ, D, float(D) ** -0.5, num_kv_heads=KVH, kv_cache_dtype="nvfp4", max_num_seqs=max(B, 1))
     builder = BE.HorizonFp4Builder()
     layer = SimpleNamespace(_k_scale_float=float(gk[0]), _v_scale_float=float(gv[0]), layer_name="layers.0.attn")
     metas = [builder.build(0, cam_of(bt)) for bt in batches]
@@ -298,13 +320,13 @@ def main():
     v_scale = float(gv[0])
 
     def decode_only(i):
-        bt, m = batches[i % 2], metas[i % 2]
+        bt, m = batches[i % NBT], metas[i % NBT]
         v = impl._cache_views(pool)
         K.decode_ragged(bt.q, v["flat"], v["strides"], PS, m.block_table, m.seq_lens, m.query_start_loc, impl.scale,
                         v_scale, gk, gv, 1, bt.out, impl._state(device)["ws"], _combine=False)
     dgraphs = []
     with torch.cuda.stream(side):
-        for i in range(2):
+        for i in range(NBT):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=side):
                 decode_only(i)
@@ -322,15 +344,15 @@ def main():
         t_end = time.perf_counter() + 0.6
         i = 0
         while time.perf_counter() < t_end:
-            graphs[i % 2].replay()
+            graphs[i % NBT].replay()
             i += 1
         for i in range(args.warmup):
-            graphs[i % 2].replay()
+            graphs[i % NBT].replay()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(args.steps):
-            graphs[i % 2].replay()
+            graphs[i % NBT].replay()
         e1.record()
         barrier()
         ms_total = e0.elapsed_time(e1)
@@ -338,11 +360,11 @@ def main():
         # ---- the decode kernel alone (roofline): graphs holding only that launch, CUDA events around K replays
         torch.cuda.synchronize()
         for i in range(args.warmup):
-            dgraphs[i % 2].replay()
+            dgraphs[i % NBT].replay()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for i in range(args.steps):
-            dgraphs[i % 2].replay()
+            dgraphs[i % NBT].replay()
         b.record()
         b.synchronize()
         dec_ms = [a.elapsed_time(b) / args.steps]
@@ -361,7 +383,7 @@ def main():
         d2h = hosts[0].out.numel() * hosts[0].out.element_size()
 
         def e2e_step(i):
-            h, d = hosts[i % 2], devs[i % 2]
+            h, d = hosts[i % NBT], devs[i % NBT]
             for name in ("q", "k", "v", "slot", "sl", "qsl", "bt"):
                 getattr(d, name).copy_(getattr(h, name), non_blocking=True)
             cam = SimpleNamespace(num_reqs=B, num_actual_tokens=B, query_start_loc=d.qsl, query_start_loc_cpu=h.qsl,
@@ -383,7 +405,7 @@ def main():
         t_end = time.perf_counter() + 0.4
         i = 0
         while time.perf_counter() < t_end:
-            graphs[i % 2].replay()
+            graphs[i % NBT].replay()
             i += 1
         torch.cuda.synchronize()
     clocks = sampler.summary()
@@ -394,19 +416,25 @@ def main():
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms, dec_ms_avg = (float(x) for x in times.cpu())
     ms_step = ms_total / args.steps
-    value = B * world / (ms_step * 1e-3)
-    e2e_value = B * world / (e2e_ms / args.steps * 1e-3)
+    n_req = cfg["B"] if cfg.get("sharded") else B * world        # requests of the whole job per step
+    value = n_req / (ms_step * 1e-3)
+    e2e_value = n_req / (e2e_ms / args.steps * 1e-3)
 
     # ---- validation: outputs gathered with NCCL (the only collective), checked on rank 0
-    for i in range(2):
+    for i in range(NBT):
         step(i)
     torch.cuda.synchronize()
     status = K.workspace_status(impl._state(device)["ws"])
     finite = bool(torch.isfinite(batches[0].out.float()).all())
     if world > 1:
-        outs = [torch.empty_like(batches[0].out) for _ in range(world)]
-        dist.all_gather(outs, batches[0].out)
-        finite = all(bool(torch.isfinite(o.float()).all()) for o in outs)
+        if cfg.get("sharded"):
+            from horizon_kernels_b200.sharding import gather_outputs
+            full = gather_outputs(batches[0].out, rows, cfg["B"])            # request order of the whole batch
+            finite = bool(torch.isfinite(full.float()).all()) and full.shape[0] == cfg["B"]
+        else:
+            outs = [torch.empty_like(batches[0].out) for _ in range(world)]
+            dist.all_gather(outs, batches[0].out)
+            finite = all(bool(torch.isfinite(o.float()).all()) for o in outs)
         st = torch.tensor([status], device=device)
         dist.all_reduce(st, op=dist.ReduceOp.MIN)
         status = int(st)
@@ -416,7 +444,7 @@ def main():
             dist.destroy_process_group()
         return
 
-    alg = algorithmic_bytes(cfg, batches[0].lens + batches[1].lens) / 2
+    alg = algorithmic_bytes(cfg, [L for bt in batches for L in bt.lens]) / NBT      # rank 0's launch
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(peaks_path):
         peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
@@ -427,13 +455,15 @@ def main():
     # bytes), scaled by the algorithmic bytes of this run's batches
     traffic = alg * TRAFFIC_RATIO.get(args.workload, float("nan")) if args.workload in TRAFFIC_RATIO else None
     line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong" if cfg.get("sharded") else "weak",
             "vs_baseline": None, "dtype": "f16 mma over e2m1 x e4m3 dequantised values, fp32 softmax and accumulation",
             "data": "synthetic",
             "config": {"workload": args.workload, **{k: cfg[k] for k in ("B", "HQ", "KVH", "D", "PS")},
-                       "context": list(cfg["law"]), "pool_pages": cfg["pool"], "per_gpu_batch": B,
+                       "context": list(cfg["law"]), "pool_pages": int(pool.shape[0]), "per_gpu_batch": B,
                        "step": "quantize-on-write of 1 new token per request + paged decode + combine, one layer",
-                       "l2": "two batches on disjoint pages alternate, each reads more cache bytes than the L2 holds",
+                       "l2": ("two batches on disjoint pages alternate, each reads more cache bytes than the L2 holds"
+                              if NBT > 1 else "one batch whose cache reads per GPU exceed the L2 several times"),
                        "timing": "CUDA-graph replay of the plugin calls, CUDA events around the K steps, max over ranks",
                        "clocks": "NVML sampled every 20 ms while the same step loops before, during and after the timed steps"},
             "tokens_per_s_per_gpu": value / world,
