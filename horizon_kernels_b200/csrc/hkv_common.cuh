@@ -124,6 +124,16 @@ __device__ __forceinline__ uint32_t lds8(uint32_t a) {
   asm volatile("ld.shared.u8 %0, [%1];" : "=r"(r) : "r"(a));
   return r;
 }
+// true in exactly one lane of a converged warp. The compiler knows that the guarded code runs in a single thread, so
+// a bulk copy inside it takes its operands from that thread without a loop over the active lanes.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ void sts64_zero(uint32_t a) {
+  asm volatile("st.shared.v2.u32 [%0], {%1, %1};" ::"r"(a), "r"(0u) : "memory");
+}
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }

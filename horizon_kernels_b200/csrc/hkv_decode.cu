@@ -41,7 +41,8 @@ struct DecodeParams {
   const uint8_t* ksf;
   const uint8_t* vd;
   const uint8_t* vsf;
-  long long dsp, dst, dsh, ssp, sst, ssh;
+  long long dsh, ssh;                                // byte strides between kv heads (codes, scales)
+  unsigned dsp, ssp;                                 // byte strides between pages (codes, scales), < 2^31
   const int* bt;
   const int* seq_lens;
   const int* qsl;
@@ -67,17 +68,22 @@ struct Geo {
 #define HKV_NS128 3
 #define HKV_MINB128 3
 #endif
+
   static constexpr int NS = D == 128 ? HKV_NS128 : 4;  // stages per warp
   static constexpr int MINB = D == 128 ? HKV_MINB128 : 2;   // CTAs per SM the register budget is sized for
   static constexpr int TILE = UT * SLOT;               // bytes of one (head, side) tile of a unit
   static constexpr int STAGE = 2 * TILE;
   static constexpr int ROW = LAYOUT == 0 ? SLOT : SD;  // byte stride between code rows in shared memory
+  static constexpr int SD_ROW = ROW;                   // .. and between the code rows of one head in the cache
   static constexpr int SF_BASE = LAYOUT == 0 ? SD : UT * SD;
   static constexpr int SF_ROW = LAYOUT == 0 ? SLOT : SS;
   static constexpr int KS = D / 16;                    // k-steps of K Q^T == mma tiles of V^T P^T (per 16 tokens)
   static constexpr int NBL = D / 64;                   // 16-channel blocks of one key row held by one lane
   static constexpr int NH = D / 128;                   // 16-channel blocks of one value row held by one lane
-  static constexpr int NCH = UB == 1 ? 2 : 1;          // independent accumulators per score tile
+#ifndef HKV_NCH128
+#define HKV_NCH128 1
+#endif
+  static constexpr int NCH = UB == 1 ? 2 : HKV_NCH128; // independent accumulators per score tile
   // token (row of a 16-token block) handled by row i of the 16-row score tile (chosen so that the value loads of a
   // warp hit distinct shared-memory banks)
   __device__ static constexpr int tok(int i) { return (D == 128 && LAYOUT == 0) ? 2 * (i & 7) + (i >> 3) : i; }
@@ -246,7 +252,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   // re-deriving them from the thread index inside the main loop.
   uint32_t ring_a = smem_u32(ring + w * NS * Gm::STAGE), bars_a = smem_u32(bars + w * NS);
   const int r0 = Gm::tok(g), r1 = Gm::tok(g + 8);
-  const int t00 = Gm::tok(2 * c), t01 = Gm::tok(2 * c + 1), t10 = Gm::tok(2 * c + 8), t11 = Gm::tok(2 * c + 9);
+  const int t00 = Gm::tok(2 * c);
   uint32_t koff_d = r0 * Gm::ROW + 8 * Gm::kblk(c, 0), koff_s = Gm::SF_BASE + r0 * Gm::SF_ROW + Gm::kblk(c, 0);
   uint32_t voff_d = Gm::TILE + t00 * Gm::ROW + 8 * g, voff_s = Gm::TILE + Gm::SF_BASE + t00 * Gm::SF_ROW + g;
   asm volatile("" : "+r"(ring_a), "+r"(bars_a), "+r"(koff_d), "+r"(koff_s), "+r"(voff_d), "+r"(voff_s));
@@ -258,8 +264,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   int f_blk = w + (int)(lo - cw.seq0);              // unit (inside the cursor's sequence) to fetch next; may run past
   int f_fast_end = 0;                               // units below this bound take the fast path
   int f_idx = 0, pg = 0;                            // page ids of the warp's next 32 blocks of the sequence, one per lane
-  unsigned f_n = 0;                                 // stages used so far
-  int f_left = n_my;                                // units still to be fetched
+  unsigned f_n = 0;                                 // units fetched so far (of n_my)
   const uint8_t* f_k = p.kd + (long long)f_h * p.dsh;
   const uint8_t* f_v = p.vd + (long long)f_h * p.dsh;
   const uint8_t* f_ks = p.ksf + (long long)f_h * p.ssh;
@@ -267,7 +272,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   const int* f_bt = p.bt + (long long)f_b * p.MP;
   const int lps = 31 - __clz(p.PS);                 // page size is a power of two
 
-  auto fetch_slow = [&]() -> bool {                 // true: the unit carries no bytes and has been dealt with here
+  auto fetch_slow = [&](const uint32_t bar) -> bool {                 // true: the unit carries no bytes and has been dealt with here
     if (f_blk >= f_U) {                             // the cursor left its sequence: walk to the one that holds the unit
       do {
         f_blk -= f_U;
@@ -286,7 +291,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       f_bt = p.bt + (long long)f_b * p.MP;
     }
     if (f_L == 0) {                                 // an empty context has one unit and nothing to read: complete the
-      if (lane == 0) mbar_arrive_u32(bars_a + 8 * (f_n % NS));   // phase with a plain arrival so that both sides stay in step
+      if (lane == 0) mbar_arrive_u32(bar);          // phase with a plain arrival so that both sides stay in step
       f_fast_end = 0;
       return true;
     }
@@ -298,44 +303,57 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
     f_fast_end = min(f_U, f_blk + (32 / UB) * TG);
     return false;
   };
-  auto fetch_one = [&]() {
+  // fetches this warp's next unit into the stage at shared address st, completion on the barrier at address bar
+  auto fetch_one = [&](const uint32_t bar, const uint32_t st) {
     bool empty = false;
-    if (f_blk >= f_fast_end) empty = fetch_slow();
+    if (f_blk >= f_fast_end) empty = fetch_slow(bar);
     if (!empty) {
-      const int page = __shfl_sync(0xffffffffu, pg, f_idx + (lane < UB ? lane : 0));
+      int page[UB];                                             // page ids of the unit's 16-token blocks (warp-uniform)
+#pragma unroll
+      for (int bi = 0; bi < UB; ++bi) page[bi] = __shfl_sync(0xffffffffu, pg, f_idx + bi);
       f_idx += UB;
       const int tok0 = f_blk * UT;
       const int nb = min(UB, (f_L - tok0 + 15) >> 4);          // 16-token blocks of this unit that exist
-      const unsigned slot = f_n % NS;
-      const uint32_t bar = bars_a + 8 * slot;
-      if (lane == 0) mbar_expect_tx_u32(bar, nb * (Gm::STAGE / UB));
-      __syncwarp();
-      if (lane < nb) {                                          // lane j copies block j of the unit
-        const int pos0 = (tok0 + 16 * lane) & (p.PS - 1);
-        const long long doff = (long long)page * p.dsp + (long long)pos0 * p.dst;
-        if (LAYOUT == 0) {
-          const uint32_t st = ring_a + slot * Gm::STAGE + lane * (16 * Gm::SLOT);
-          bulk_g2s_u32(st, f_k + doff, 16 * Gm::SLOT, bar);
-          bulk_g2s_u32(st + Gm::TILE, f_v + doff, 16 * Gm::SLOT, bar);
-        } else {
-          const long long soff = (long long)page * p.ssp + (long long)pos0 * p.sst;
-          const uint32_t st = ring_a + slot * Gm::STAGE + lane * (16 * Gm::SD);
-          const uint32_t ss = ring_a + slot * Gm::STAGE + UT * Gm::SD + lane * (16 * Gm::SS);
-          bulk_g2s_u32(st, f_k + doff, 16 * Gm::SD, bar);
-          bulk_g2s_u32(ss, f_ks + soff, 16 * Gm::SS, bar);
-          bulk_g2s_u32(st + Gm::TILE, f_v + doff, 16 * Gm::SD, bar);
-          bulk_g2s_u32(ss + Gm::TILE, f_vs + soff, 16 * Gm::SS, bar);
+      if (elect_one()) {                                        // one lane arms the barrier and issues the copies
+        mbar_expect_tx_u32(bar, nb * (Gm::STAGE / UB));
+#pragma unroll
+        for (int bi = 0; bi < UB; ++bi) {
+          if (bi < nb) {
+            const unsigned pos0 = (unsigned)(tok0 + 16 * bi) & (unsigned)(p.PS - 1);
+            const unsigned long long doff = (unsigned long long)(unsigned)page[bi] * p.dsp + pos0 * (unsigned)Gm::SD_ROW;
+            if (LAYOUT == 0) {
+              bulk_g2s_u32(st + bi * (16 * Gm::SLOT), f_k + doff, 16 * Gm::SLOT, bar);
+              bulk_g2s_u32(st + bi * (16 * Gm::SLOT) + Gm::TILE, f_v + doff, 16 * Gm::SLOT, bar);
+            } else {
+              const unsigned long long soff = (unsigned long long)(unsigned)page[bi] * p.ssp + pos0 * (unsigned)Gm::SS;
+              const uint32_t sd = st + bi * (16 * Gm::SD), ss = st + UT * Gm::SD + bi * (16 * Gm::SS);
+              bulk_g2s_u32(sd, f_k + doff, 16 * Gm::SD, bar);
+              bulk_g2s_u32(ss, f_ks + soff, 16 * Gm::SS, bar);
+              bulk_g2s_u32(sd + Gm::TILE, f_v + doff, 16 * Gm::SD, bar);
+              bulk_g2s_u32(ss + Gm::TILE, f_vs + soff, 16 * Gm::SS, bar);
+            }
+          }
         }
       }
     }
     f_blk += TG;
     ++f_n;
-    --f_left;
   };
 
   unsigned c_n = 0;                                 // stages consumed so far
+  uint32_t c_bar = bars_a, c_st = ring_a, c_par = 0;  // barrier, stage and phase parity of the next stage to consume
+  auto advance = [&]() {
+    ++c_n;
+    c_bar += 8;
+    c_st += Gm::STAGE;
+    if (c_bar == bars_a + 8 * NS) {
+      c_bar = bars_a;
+      c_st = ring_a;
+      c_par ^= 1;
+    }
+  };
   bool dead = false;                                // a bounded wait ran out: stop consuming
-  while (f_n < NS && f_left > 0) fetch_one();
+  while (f_n < NS && (int)f_n < n_my) fetch_one(bars_a + 8 * f_n, ring_a + f_n * Gm::STAGE);
 
   // ---- compute side: walk the pieces of the partition
   long long pos = lo;
@@ -404,151 +422,177 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       float mneg0 = -m0 * sc, mneg1 = -m1 * sc;      // p = 2^(s * sc + mneg)
       float thr0 = m0 + tau_raw, thr1 = m1 + tau_raw;
 
-      for (int blk = blk_first; blk < blk_end; blk += TG) {
-        const unsigned slot = c_n % NS;
-        if (!mbar_try_wait_u32(bars_a + 8 * slot, (c_n / NS) & 1)) {
-          if (!mbar_wait_bounded_u32(bars_a + 8 * slot, (c_n / NS) & 1)) {
+      // waits (bounded) for the next stage this warp consumes; false once a wait ran out
+      // (the stage's addresses come back in bar and st: the unit fetched after it reuses them)
+      auto wait_stage = [&](uint32_t& bar, uint32_t& st) -> bool {
+        if (!mbar_try_wait_u32(c_bar, c_par)) {
+          if (!mbar_wait_bounded_u32(c_bar, c_par)) {
             if (lane == 0) atomicExch(&hdr->status, HKV_ERR_DEVICE_WAIT);
             dead = true;
-            break;
+            return false;
           }
         }
-        ++c_n;
-        if (L > 0) {                                  // (the single unit of an empty context carries nothing)
-          const uint32_t st = ring_a + slot * Gm::STAGE;
-          const uint32_t kd_ = st + koff_d, ks_ = st + koff_s, vd_ = st + voff_d, vs_ = st + voff_s;
-          const bool masked = blk >= blk_mask;        // warp-uniform: only the last unit(s) of a sequence
+        bar = c_bar;
+        st = c_st;
+        advance();
+        return true;
+      };
 
-          // ---------------- S^T = K Q^T per 16-token block: rows = tokens, columns = query rows
-          float x[UB][4];
+      // ---------------- S^T = K Q^T per 16-token block: rows = tokens, columns = query rows
+      auto k_phase = [&](const uint32_t st, float (&x)[UB][4]) {
+        const uint32_t kd_ = st + koff_d, ks_ = st + koff_s;
 #pragma unroll
-          for (int bi = 0; bi < UB; ++bi) {
-            float sa[Gm::NCH][4];
+        for (int bi = 0; bi < UB; ++bi) {
+          float sa[Gm::NCH][4];
 #pragma unroll
-            for (int i = 0; i < Gm::NCH; ++i) sa[i][0] = sa[i][1] = sa[i][2] = sa[i][3] = 0.0f;
+          for (int i = 0; i < Gm::NCH; ++i) sa[i][0] = sa[i][1] = sa[i][2] = sa[i][3] = 0.0f;
 #pragma unroll
-            for (int u = 0; u < Gm::NBL; ++u) {
-              const int du = bi * 16 * Gm::ROW + 8 * (Gm::kblk(0, u) - Gm::kblk(0, 0));
-              const int su = bi * 16 * Gm::SF_ROW + Gm::kblk(0, u) - Gm::kblk(0, 0);
-              const uint2 w0 = lds64(kd_ + du);
-              const uint2 w1 = lds64(kd_ + du + KR1 * Gm::ROW);
-              const uint32_t f0 = lds8(ks_ + su), f1 = lds8(ks_ + su + KR1 * Gm::SF_ROW);
-              const __half2 sf = u32_as_h2(e4m3x2_to_f16x2(f0 | (f1 << 8)));   // (scale of row r0, scale of row r1)
-              const __half2 sf0 = __low2half2(sf), sf1 = __high2half2(sf);
-              uint32_t e0[4], e1[4], e2[4], e3[4];
-              e2m1x8_to_f16x2(w0.x, e0);
-              e2m1x8_to_f16x2(w0.y, e1);
-              e2m1x8_to_f16x2(w1.x, e2);
-              e2m1x8_to_f16x2(w1.y, e3);
-              // k-step v of this block: A = {row r0 k-low, row r1 k-low, row r0 k-high, row r1 k-high}
-              mma_f16(sa[0], hmul2h(e0[0], sf0), hmul2h(e2[0], sf1), hmul2h(e0[1], sf0), hmul2h(e2[1], sf1),
-                      qa[4 * u + 0][0], qa[4 * u + 0][1]);
-              mma_f16(sa[Gm::NCH - 1], hmul2h(e0[2], sf0), hmul2h(e2[2], sf1), hmul2h(e0[3], sf0), hmul2h(e2[3], sf1),
-                      qa[4 * u + 1][0], qa[4 * u + 1][1]);
-              mma_f16(sa[0], hmul2h(e1[0], sf0), hmul2h(e3[0], sf1), hmul2h(e1[1], sf0), hmul2h(e3[1], sf1),
-                      qa[4 * u + 2][0], qa[4 * u + 2][1]);
-              mma_f16(sa[Gm::NCH - 1], hmul2h(e1[2], sf0), hmul2h(e3[2], sf1), hmul2h(e1[3], sf0), hmul2h(e3[3], sf1),
-                      qa[4 * u + 3][0], qa[4 * u + 3][1]);
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) x[bi][i] = Gm::NCH == 2 ? sa[0][i] + sa[Gm::NCH - 1][i] : sa[0][i];
+          for (int u = 0; u < Gm::NBL; ++u) {
+            const int du = bi * 16 * Gm::ROW + 8 * (Gm::kblk(0, u) - Gm::kblk(0, 0));
+            const int su = bi * 16 * Gm::SF_ROW + Gm::kblk(0, u) - Gm::kblk(0, 0);
+            const uint2 w0 = lds64(kd_ + du);
+            const uint2 w1 = lds64(kd_ + du + KR1 * Gm::ROW);
+            const uint32_t f0 = lds8(ks_ + su), f1 = lds8(ks_ + su + KR1 * Gm::SF_ROW);
+            const __half2 sf = u32_as_h2(e4m3x2_to_f16x2(f0 | (f1 << 8)));   // (scale of row r0, scale of row r1)
+            const __half2 sf0 = __low2half2(sf), sf1 = __high2half2(sf);
+            uint32_t e0[4], e1[4], e2[4], e3[4];
+            e2m1x8_to_f16x2(w0.x, e0);
+            e2m1x8_to_f16x2(w0.y, e1);
+            e2m1x8_to_f16x2(w1.x, e2);
+            e2m1x8_to_f16x2(w1.y, e3);
+            // k-step v of this block: A = {row r0 k-low, row r1 k-low, row r0 k-high, row r1 k-high}
+            mma_f16(sa[0], hmul2h(e0[0], sf0), hmul2h(e2[0], sf1), hmul2h(e0[1], sf0), hmul2h(e2[1], sf1),
+                    qa[4 * u + 0][0], qa[4 * u + 0][1]);
+            mma_f16(sa[Gm::NCH - 1], hmul2h(e0[2], sf0), hmul2h(e2[2], sf1), hmul2h(e0[3], sf0), hmul2h(e2[3], sf1),
+                    qa[4 * u + 1][0], qa[4 * u + 1][1]);
+            mma_f16(sa[0], hmul2h(e1[0], sf0), hmul2h(e3[0], sf1), hmul2h(e1[1], sf0), hmul2h(e3[1], sf1),
+                    qa[4 * u + 2][0], qa[4 * u + 2][1]);
+            mma_f16(sa[Gm::NCH - 1], hmul2h(e1[2], sf0), hmul2h(e3[2], sf1), hmul2h(e1[3], sf0), hmul2h(e3[3], sf1),
+                    qa[4 * u + 3][0], qa[4 * u + 3][1]);
           }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) x[bi][i] = Gm::NCH == 2 ? sa[0][i] + sa[Gm::NCH - 1][i] : sa[0][i];
+        }
+      };
 
-          // ---------------- online softmax (raw score units): this lane holds query rows 2c, 2c+1 of tokens r0, r1
-          // of every block; x[bi] = {(r0, row 2c), (r0, row 2c+1), (r1, row 2c), (r1, row 2c+1)}
-          const int tbase = blk * UT;
-          if (masked) {
-            const float ninf = -__int_as_float(0x7f800000);
+      // ---------------- online softmax (raw score units): this lane holds query rows 2c, 2c+1 of tokens r0, r1 of
+      // every block; x[bi] = {(r0, row 2c), (r0, row 2c+1), (r1, row 2c), (r1, row 2c+1)}. Leaves P^T as the B
+      // operand of the second product in pb.
+      auto softmax = [&](const uint32_t st, const int blk, float (&x)[UB][4], uint32_t (&pb)[UB][2]) {
+        const int tbase = blk * UT;
+        if (blk >= blk_mask) {                        // warp-uniform: only the last unit(s) of a sequence
+          // rows past the context hold arbitrary bytes: their scores become -inf below, and their value scales are
+          // set to zero here, in shared memory, so that the value product needs no masking code
+          if (lane < UT && tbase + lane >= L) {
+            const uint32_t a = st + Gm::TILE + Gm::SF_BASE + lane * Gm::SF_ROW;
 #pragma unroll
-            for (int bi = 0; bi < UB; ++bi) {
-              const int ta = tbase + 16 * bi + r0, tb = tbase + 16 * bi + r1;
-              x[bi][0] = ta < lim0 ? x[bi][0] : ninf;
-              x[bi][1] = ta < lim1 ? x[bi][1] : ninf;
-              x[bi][2] = tb < lim0 ? x[bi][2] : ninf;
-              x[bi][3] = tb < lim1 ? x[bi][3] : ninf;
-            }
-          }
-          // the running max moves only when some score exceeds it by more than TAU (then P stays below 2^TAU, inside
-          // f16); the cross-lane maximum is needed only in that case
-          float bm0 = fmaxf(x[0][0], x[0][2]), bm1 = fmaxf(x[0][1], x[0][3]);
-#pragma unroll
-          for (int bi = 1; bi < UB; ++bi) {
-            bm0 = fmaxf(bm0, fmaxf(x[bi][0], x[bi][2]));
-            bm1 = fmaxf(bm1, fmaxf(x[bi][1], x[bi][3]));
-          }
-          if (__any_sync(0xffffffffu, (bm0 > thr0) | (bm1 > thr1))) {
-#pragma unroll
-            for (int of = 4; of < 32; of <<= 1) {
-              bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, of));
-              bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, of));
-            }
-            const float n0 = fmaxf(m0, fmaxf(bm0, NEG_BIG)), n1 = fmaxf(m1, fmaxf(bm1, NEG_BIG));
-            const float al0 = fast_exp2((m0 - n0) * sc), al1 = fast_exp2((m1 - n1) * sc);
-            m0 = n0; m1 = n1;
-            mneg0 = -n0 * sc; mneg1 = -n1 * sc;
-            thr0 = n0 + tau_raw; thr1 = n1 + tau_raw;
-            l0 *= al0; l1 *= al1;
-#pragma unroll
-            for (int j = 0; j < Gm::KS; ++j) {
-              o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1;
-            }
-          }
-          uint32_t pb[UB][2];                         // P^T as the B operand of the second product
-#pragma unroll
-          for (int bi = 0; bi < UB; ++bi) {
-            const float p00 = fast_exp2(fmaf(x[bi][0], sc, mneg0)), p01 = fast_exp2(fmaf(x[bi][1], sc, mneg1)),
-                        p10 = fast_exp2(fmaf(x[bi][2], sc, mneg0)), p11 = fast_exp2(fmaf(x[bi][3], sc, mneg1));
-            l0 += p00 + p10;
-            l1 += p01 + p11;
-            // transpose the two 8x8 (token, row) tiles
-            pb[bi][0] = movmatrix_trans(pack_f16x2(p00, p01));
-            pb[bi][1] = movmatrix_trans(pack_f16x2(p10, p11));
-          }
-
-          // ---------------- O^T += V^T P^T : rows = channels of block g (+8), columns = query rows
-          const int nvalid = L - tbase;               // >= UT unless this is the sequence's last unit
-#pragma unroll
-          for (int bi = 0; bi < UB; ++bi) {
-#pragma unroll
-            for (int hf = 0; hf < Gm::NH; ++hf) {
-              const int dv = bi * 16 * Gm::ROW + 64 * hf, sv = bi * 16 * Gm::SF_ROW + 8 * hf;
-              const uint2 v00 = lds64(vd_ + dv);
-              const uint2 v01 = lds64(vd_ + dv + VR01 * Gm::ROW);
-              const uint2 v10 = lds64(vd_ + dv + VR10 * Gm::ROW);
-              const uint2 v11 = lds64(vd_ + dv + VR11 * Gm::ROW);
-              uint32_t f00 = lds8(vs_ + sv), f01 = lds8(vs_ + sv + VR01 * Gm::SF_ROW);
-              uint32_t f10 = lds8(vs_ + sv + VR10 * Gm::SF_ROW), f11 = lds8(vs_ + sv + VR11 * Gm::SF_ROW);
-              if (masked) {                           // rows past the context hold arbitrary bytes: read them as 0
-                f00 = 16 * bi + t00 < nvalid ? f00 : 0u;
-                f01 = 16 * bi + t01 < nvalid ? f01 : 0u;
-                f10 = 16 * bi + t10 < nvalid ? f10 : 0u;
-                f11 = 16 * bi + t11 < nvalid ? f11 : 0u;
-              }
-              const __half2 sa = u32_as_h2(e4m3x2_to_f16x2(f00 | (f01 << 8))),
-                            sb = u32_as_h2(e4m3x2_to_f16x2(f10 | (f11 << 8)));
-              const uint32_t M = 0x0f0f0f0fu;
-#pragma unroll
-              for (int wv = 0; wv < 2; ++wv) {
-                const uint32_t a0 = wv ? v00.y : v00.x, a1 = wv ? v01.y : v01.x, b0_ = wv ? v10.y : v10.x,
-                               b1_ = wv ? v11.y : v11.x;
-                // bytes of (token pair, channel): low nibble = first token of the pair, high nibble = second
-                const uint32_t xe = (a0 & M) | ((a1 * 16u) & ~M), xo = ((a0 >> 4) & M) | (a1 & ~M);
-                const uint32_t ye = (b0_ & M) | ((b1_ * 16u) & ~M), yo = ((b0_ >> 4) & M) | (b1_ & ~M);
-                uint32_t ae[4], ao[4], be[4], bo[4]; // [channel pair] -> f16x2 over (first, second) token
-                e2m1x8_to_f16x2(xe, ae);
-                e2m1x8_to_f16x2(xo, ao);
-                e2m1x8_to_f16x2(ye, be);
-                e2m1x8_to_f16x2(yo, bo);
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                  mma_f16(o[8 * hf + 4 * wv + i], hmul2h(ae[i], sa), hmul2h(ao[i], sa), hmul2h(be[i], sb),
-                          hmul2h(bo[i], sb), pb[bi][0], pb[bi][1]);
-              }
-            }
+            for (int i = 0; i < Gm::SS; i += 8) sts64_zero(a + i);
+            fence_proxy_async();                      // the stage's next bulk copy overwrites these bytes
           }
           __syncwarp();
+          const float ninf = -__int_as_float(0x7f800000);
+#pragma unroll
+          for (int bi = 0; bi < UB; ++bi) {
+            const int ta = tbase + 16 * bi + r0, tb = tbase + 16 * bi + r1;
+            x[bi][0] = ta < lim0 ? x[bi][0] : ninf;
+            x[bi][1] = ta < lim1 ? x[bi][1] : ninf;
+            x[bi][2] = tb < lim0 ? x[bi][2] : ninf;
+            x[bi][3] = tb < lim1 ? x[bi][3] : ninf;
+          }
         }
-        if (f_left > 0) fetch_one();
+        // the running max moves only when some score exceeds it by more than TAU (then P stays below 2^TAU, inside
+        // f16); the cross-lane maximum is needed only in that case
+        float bm0 = fmaxf(x[0][0], x[0][2]), bm1 = fmaxf(x[0][1], x[0][3]);
+#pragma unroll
+        for (int bi = 1; bi < UB; ++bi) {
+          bm0 = fmaxf(bm0, fmaxf(x[bi][0], x[bi][2]));
+          bm1 = fmaxf(bm1, fmaxf(x[bi][1], x[bi][3]));
+        }
+        if (__any_sync(0xffffffffu, (bm0 > thr0) | (bm1 > thr1))) {
+#pragma unroll
+          for (int of = 4; of < 32; of <<= 1) {
+            bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, of));
+            bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, of));
+          }
+          const float n0 = fmaxf(m0, fmaxf(bm0, NEG_BIG)), n1 = fmaxf(m1, fmaxf(bm1, NEG_BIG));
+          const float al0 = fast_exp2((m0 - n0) * sc), al1 = fast_exp2((m1 - n1) * sc);
+          m0 = n0; m1 = n1;
+          mneg0 = -n0 * sc; mneg1 = -n1 * sc;
+          thr0 = n0 + tau_raw; thr1 = n1 + tau_raw;
+          l0 *= al0; l1 *= al1;
+#pragma unroll
+          for (int j = 0; j < Gm::KS; ++j) {
+            o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1;
+          }
+        }
+#pragma unroll
+        for (int bi = 0; bi < UB; ++bi) {
+          const float p00 = fast_exp2(fmaf(x[bi][0], sc, mneg0)), p01 = fast_exp2(fmaf(x[bi][1], sc, mneg1)),
+                      p10 = fast_exp2(fmaf(x[bi][2], sc, mneg0)), p11 = fast_exp2(fmaf(x[bi][3], sc, mneg1));
+          l0 += p00 + p10;
+          l1 += p01 + p11;
+          // transpose the two 8x8 (token, row) tiles
+          pb[bi][0] = movmatrix_trans(pack_f16x2(p00, p01));
+          pb[bi][1] = movmatrix_trans(pack_f16x2(p10, p11));
+        }
+      };
+
+      // ---------------- O^T += V^T P^T : rows = channels of block g (+8), columns = query rows
+      auto v_phase = [&](const uint32_t st, const uint32_t (&pb)[UB][2]) {
+        const uint32_t vd_ = st + voff_d, vs_ = st + voff_s;
+#pragma unroll
+        for (int bi = 0; bi < UB; ++bi) {
+#pragma unroll
+          for (int hf = 0; hf < Gm::NH; ++hf) {
+            const int dv = bi * 16 * Gm::ROW + 64 * hf, sv = bi * 16 * Gm::SF_ROW + 8 * hf;
+            const uint2 v00 = lds64(vd_ + dv);
+            const uint2 v01 = lds64(vd_ + dv + VR01 * Gm::ROW);
+            const uint2 v10 = lds64(vd_ + dv + VR10 * Gm::ROW);
+            const uint2 v11 = lds64(vd_ + dv + VR11 * Gm::ROW);
+            const uint32_t f00 = lds8(vs_ + sv), f01 = lds8(vs_ + sv + VR01 * Gm::SF_ROW);
+            const uint32_t f10 = lds8(vs_ + sv + VR10 * Gm::SF_ROW), f11 = lds8(vs_ + sv + VR11 * Gm::SF_ROW);
+            const __half2 sa = u32_as_h2(e4m3x2_to_f16x2(f00 | (f01 << 8))),
+                          sb = u32_as_h2(e4m3x2_to_f16x2(f10 | (f11 << 8)));
+            const uint32_t M = 0x0f0f0f0fu;
+#pragma unroll
+            for (int wv = 0; wv < 2; ++wv) {
+              const uint32_t a0 = wv ? v00.y : v00.x, a1 = wv ? v01.y : v01.x, b0_ = wv ? v10.y : v10.x,
+                             b1_ = wv ? v11.y : v11.x;
+              // bytes of (token pair, channel): low nibble = first token of the pair, high nibble = second
+              const uint32_t xe = (a0 & M) | ((a1 * 16u) & ~M), xo = ((a0 >> 4) & M) | (a1 & ~M);
+              const uint32_t ye = (b0_ & M) | ((b1_ * 16u) & ~M), yo = ((b0_ >> 4) & M) | (b1_ & ~M);
+              uint32_t ae[4], ao[4], be[4], bo[4];   // [channel pair] -> f16x2 over (first, second) token
+              e2m1x8_to_f16x2(xe, ae);
+              e2m1x8_to_f16x2(xo, ao);
+              e2m1x8_to_f16x2(ye, be);
+              e2m1x8_to_f16x2(yo, bo);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                mma_f16(o[8 * hf + 4 * wv + i], hmul2h(ae[i], sa), hmul2h(ao[i], sa), hmul2h(be[i], sb),
+                        hmul2h(bo[i], sb), pb[bi][0], pb[bi][1]);
+            }
+          }
+        }
+      };
+
+      uint32_t bar, st;
+      if (L == 0) {                                   // the single unit of an empty context carries nothing
+        for (int blk = blk_first; blk < blk_end; blk += TG) {
+          if (!wait_stage(bar, st)) break;
+          if ((int)f_n < n_my) fetch_one(bar, st);
+        }
+      } else if (wait_stage(bar, st)) {
+        for (int blk = blk_first;;) {
+          float x[UB][4];
+          uint32_t pb[UB][2];
+          k_phase(st, x);
+          softmax(st, blk, x, pb);
+          v_phase(st, pb);
+          __syncwarp();
+          if ((int)f_n < n_my) fetch_one(bar, st);
+          blk += TG;
+          if (blk >= blk_end || !wait_stage(bar, st)) break;
+        }
       }
     }
 
@@ -613,7 +657,10 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   // a warp that gave up may still have copies in flight: wait for them (bounded) before the CTA's shared memory is
   // released
   if (dead) {
-    for (unsigned i = c_n; i < f_n; ++i) (void)mbar_wait_bounded_u32(bars_a + 8 * (i % NS), (i / NS) & 1);
+    while (c_n < f_n) {
+      (void)mbar_wait_bounded_u32(c_bar, c_par);
+      advance();
+    }
   }
 }
 
@@ -766,6 +813,7 @@ extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const 
     return HKV_ERR_UNSUPPORTED;                      // token rows of a head are not contiguous (positions-outer pages)
   if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kd | (uintptr_t)vd) & 15) return HKV_ERR_ALIGN;
   if ((dsp | dsh) & 15) return HKV_ERR_ALIGN;
+  if (dsp < 0 || ssp < 0 || dsp >= (1ll << 31) || ssp >= (1ll << 31)) return HKV_ERR_RANGE;   // a page is far below 2 GB
   if (layout == 1 && ((((uintptr_t)ksf | (uintptr_t)vsf) & 15) || ((ssp | ssh) & 15))) return HKV_ERR_ALIGN;
   if ((uintptr_t)workspace & 255) return HKV_ERR_ALIGN;
   DeviceInfo* di;
@@ -781,7 +829,7 @@ extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const 
   DecodeParams p;
   p.q = (const __nv_bfloat16*)q;
   p.kd = (const uint8_t*)kd; p.ksf = (const uint8_t*)ksf; p.vd = (const uint8_t*)vd; p.vsf = (const uint8_t*)vsf;
-  p.dsp = dsp; p.dst = dst; p.dsh = dsh; p.ssp = ssp; p.sst = sst; p.ssh = ssh;
+  p.dsp = (unsigned)dsp; p.dsh = dsh; p.ssp = (unsigned)ssp; p.ssh = ssh;
   p.bt = block_tables; p.seq_lens = seq_lens; p.qsl = query_start_loc;
   p.gk = gk; p.gv = gv;
   p.ws = (uint8_t*)workspace;
