@@ -314,7 +314,23 @@ def main():
             with torch.cuda.graph(g, stream=side):
                 step(i)
             graphs.append(g)
+        # a serving engine captures all layers of a model in one graph: CHAIN consecutive steps (alternating batches)
+        # in one graph, so that a step's launches follow the previous step's without a graph boundary in between
+        CHAIN = 5 * NBT
+        chain_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(chain_graph, stream=side):
+            for i in range(CHAIN):
+                step(i)
     torch.cuda.synchronize()
+
+    def replay_steps(n, first=0):
+        i = first
+        while n - (i - first) >= CHAIN and i % NBT == 0:
+            chain_graph.replay()
+            i += CHAIN
+        while i - first < n:
+            graphs[i % NBT].replay()
+            i += 1
 
     # graphs holding only the decode launch, for the roofline timing of that kernel
     v_scale = float(gv[0])
@@ -324,13 +340,11 @@ def main():
         v = impl._cache_views(pool)
         K.decode_ragged(bt.q, v["flat"], v["strides"], PS, m.block_table, m.seq_lens, m.query_start_loc, impl.scale,
                         v_scale, gk, gv, 1, bt.out, impl._state(device)["ws"], _combine=False)
-    dgraphs = []
+    dgraph = torch.cuda.CUDAGraph()                  # args.steps launches back to back, alternating batches
     with torch.cuda.stream(side):
-        for i in range(NBT):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
+        with torch.cuda.graph(dgraph, stream=side):
+            for i in range(max(args.steps, 1)):
                 decode_only(i)
-            dgraphs.append(g)
     torch.cuda.synchronize()
 
     def barrier():
@@ -351,23 +365,20 @@ def main():
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(args.steps):
-            graphs[i % NBT].replay()
+        replay_steps(args.steps)
         e1.record()
         barrier()
         ms_total = e0.elapsed_time(e1)
 
         # ---- the decode kernel alone (roofline): graphs holding only that launch, CUDA events around K replays
         torch.cuda.synchronize()
-        for i in range(args.warmup):
-            dgraphs[i % NBT].replay()
+        dgraph.replay()                                  # warm-up: the same args.steps launches
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for i in range(args.steps):
-            dgraphs[i % NBT].replay()
+        dgraph.replay()
         b.record()
         b.synchronize()
-        dec_ms = [a.elapsed_time(b) / args.steps]
+        dec_ms = [a.elapsed_time(b) / max(args.steps, 1)]
 
         # ---- end to end: host inputs -> pinned H2D copies -> write + decode + combine -> D2H of the output
         pin = lambda t: t.cpu().pin_memory()  # noqa: E731
@@ -464,7 +475,9 @@ def main():
                        "step": "quantize-on-write of 1 new token per request + paged decode + combine, one layer",
                        "l2": ("two batches on disjoint pages alternate, each reads more cache bytes than the L2 holds"
                               if NBT > 1 else "one batch whose cache reads per GPU exceed the L2 several times"),
-                       "timing": "CUDA-graph replay of the plugin calls, CUDA events around the K steps, max over ranks",
+                       "timing": ("CUDA graphs of the plugin calls (5 steps per batch chained in one graph, like the layers "
+                                  "of a model), CUDA events around the K steps, max over ranks; roofline: K decode "
+                                  "launches back to back in one graph, CUDA events around it, divided by K"),
                        "clocks": "NVML sampled every 20 ms while the same step loops before, during and after the timed steps"},
             "tokens_per_s_per_gpu": value / world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

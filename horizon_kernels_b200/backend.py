@@ -234,6 +234,11 @@ def _build_classes():
             (reference backend.py:263-277)"""
             key = (str(device), self.num_kv_heads, self.G, self.head_size, self.qlmax)
             st = _STATE.get(key)
+            if not _STATE.get("options"):
+                # vLLM writes seq_lens and query_start_loc once per step, before the first layer runs, so the decode
+                # kernel may read them ahead of its launch dependency (HORIZON_KVFP4_EARLY_META=0 turns this off)
+                K.set_option(K.OPT_EARLY_METADATA, 0 if os.environ.get("HORIZON_KVFP4_EARLY_META", "1") == "0" else 1)
+                _STATE["options"] = True
             if st is None or st["max_reqs"] < self.max_reqs:
                 st = _STATE[key] = {"ws": K.alloc_workspace(self.max_reqs, self.num_kv_heads, self.G, self.head_size,
                                                             self.qlmax, device), "max_reqs": self.max_reqs}

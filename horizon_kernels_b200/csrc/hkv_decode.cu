@@ -24,6 +24,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "hkv_common.cuh"
 
@@ -51,6 +52,7 @@ struct DecodeParams {
   uint8_t* ws;
   __nv_bfloat16* out;
   int MP, B, KVH, G, qlmax, PS;
+  int early_meta;                                    // seq_lens / query_start_loc are read before the launch dependency
   float scale_log2, v_scale;
 };
 
@@ -141,8 +143,11 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   float* opart_ws = reinterpret_cast<float*>(p.ws + wl.opart_off);
 
   if (tid < TG * NS) mbar_init(bars + tid, 1);
-  pdl_wait();                                     // every global input may come from the preceding launch
-  pdl_launch_dependents();
+  // Every global input may come from the preceding launch, so the kernel waits for it here. The caller may state that
+  // the request metadata is older than that launch (hkv_set_option): then the partition search below, which reads only
+  // seq_lens and query_start_loc, runs while the preceding launch is still draining, and the wait comes after it.
+  const bool early = p.early_meta != 0;
+  if (!early) pdl_wait();
 
   // ---- coarse prefix of units per request: coarse[k] = sum of U_b over b < 32 k
   const int ngrp = (B + 31) >> 5;
@@ -185,13 +190,17 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   const int per = (int)max(1ll, (total + n_parts - 1) / n_parts);
   const long long lo = (long long)part * per;
   const long long hi = min(total, lo + per);
-  if (part == 0 && tid == 0) {
-    hdr->n_parts = n_parts;
-    hdr->per = per;
-    hdr->total = (int)total;
-  }
-  if (lo >= hi) {
-    if (tid == 0) descs[part].b = -1;
+  if (lo >= hi) {                                   // an idle partition
+    if (early) pdl_wait();
+    pdl_launch_dependents();
+    if (tid == 0) {
+      if (part == 0) {
+        hdr->n_parts = n_parts;
+        hdr->per = per;
+        hdr->total = (int)total;
+      }
+      descs[part].b = -1;
+    }
     return;
   }
   const int n_units = (int)(hi - lo);
@@ -339,6 +348,14 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
     f_blk += TG;
     ++f_n;
   };
+
+  if (early) pdl_wait();                            // from here on: workspace writes, block tables, cache and query reads
+  pdl_launch_dependents();
+  if (part == 0 && tid == 0) {
+    hdr->n_parts = n_parts;
+    hdr->per = per;
+    hdr->total = (int)total;
+  }
 
   unsigned c_n = 0;                                 // stages consumed so far
   uint32_t c_bar = bars_a, c_st = ring_a, c_par = 0;  // barrier, stage and phase parity of the next stage to consume
@@ -739,6 +756,7 @@ struct DeviceInfo {
   bool ready = false;
 };
 static DeviceInfo g_dev[64];
+static std::atomic<int> g_early_metadata{0};
 
 template <int D, int LAYOUT>
 static cudaError_t setup_variant(int& ctas) {
@@ -835,6 +853,7 @@ extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const 
   p.ws = (uint8_t*)workspace;
   p.out = (__nv_bfloat16*)out;
   p.MP = MP; p.B = B; p.KVH = KVH; p.G = G; p.qlmax = qlmax; p.PS = PS;
+  p.early_meta = g_early_metadata.load(std::memory_order_relaxed);
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.v_scale = v_scale;
   cudaStream_t st = (cudaStream_t)stream;
@@ -868,6 +887,14 @@ extern "C" int hkv_combine(const void* workspace, size_t workspace_bytes, const 
       D == 128 ? combine_kernel<128> : combine_kernel<256>;
   return record_cuda(launch_pdl(k, dim3(grid), dim3(128), 0, st, (const uint8_t*)workspace, (const int*)query_start_loc,
                                 (__nv_bfloat16*)out, KVH, G, qlmax, v_scale));
+}
+
+extern "C" int hkv_set_option(int option, int value) {
+  using namespace hkv;
+  if (option != HKV_OPT_EARLY_METADATA) return HKV_ERR_UNSUPPORTED;
+  if (value != 0 && value != 1) return HKV_ERR_RANGE;
+  g_early_metadata.store(value, std::memory_order_relaxed);
+  return HKV_OK;
 }
 
 extern "C" int hkv_workspace_status(void* workspace, int* status, void* stream) {

@@ -123,6 +123,15 @@ def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_
     return out
 
 
+OPT_EARLY_METADATA = 1
+
+
+def set_option(option: int, value: int) -> None:
+    """process-wide library options (include/hkv.h `hkv_set_option`). OPT_EARLY_METADATA = 1 tells the decode kernel that
+    seq_lens and query_start_loc are older than the kernel launched just before it, as they are in a serving engine."""
+    _lib.check(_lib.load().hkv_set_option(int(option), int(value)), "hkv_set_option")
+
+
 def workspace_status(workspace) -> int:
     """device status word of the last launches (0 = ok); synchronises, for tests and debugging"""
     st = C.c_int(0)

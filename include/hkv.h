@@ -121,6 +121,19 @@ int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf, const voi
                        float v_scale, const float* gk, const float* gv, int splits, void* out, void* stream);
 
 /*
+ * Process-wide options. No counterpart in the reference.
+ *   HKV_OPT_EARLY_METADATA (0 = off, the default; 1 = on): the caller states that `seq_lens` and `query_start_loc` of
+ *     every later hkv_decode / hkv_decode_noalloc call are complete before the kernel that PRECEDES the call on its
+ *     stream starts (an inference engine writes them once per step, long before the attention layers run; hkv_write never
+ *     writes them). hkv_decode then reads these two arrays while the preceding kernel is still running and waits for
+ *     it only afterwards, before it touches the block tables, the cache, the queries or the workspace. With the option
+ *     off every input may be produced by the directly preceding kernel.
+ * Returns HKV_ERR_UNSUPPORTED for an unknown option and HKV_ERR_RANGE for a value outside its set.
+ */
+#define HKV_OPT_EARLY_METADATA 1
+int hkv_set_option(int option, int value);
+
+/*
  * Copies the workspace's device status word to *status (HKV_OK or HKV_ERR_DEVICE_WAIT) and clears it. Synchronises the
  * stream: a debugging aid, not for the hot path.
  */

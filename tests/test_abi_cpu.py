@@ -87,6 +87,13 @@ def test_combine_rejects_misuse(lib):
     assert lib.hkv_combine(one, 1 << 20, one, 4, 8, 9, 128, 1, 1.0, one, None) == -3
 
 
+def test_set_option_codes(lib):
+    assert lib.hkv_set_option(99, 1) == -3
+    assert lib.hkv_set_option(1, 2) == -6
+    assert lib.hkv_set_option(1, 1) == 0
+    assert lib.hkv_set_option(1, 0) == 0
+
+
 def test_python_wrappers_refuse_cpu_tensors():
     import torch
     from horizon_kernels_b200 import kernels as K

@@ -128,6 +128,32 @@ def test_two_query_tokens_causal():
     assert_close(out, ref)
 
 
+def test_early_metadata_option_changes_nothing():
+    """with HKV_OPT_EARLY_METADATA the kernel reads seq_lens / query_start_loc ahead of its launch dependency; when they
+    are old enough (here: written long before, a synchronize in between) the output is bit-identical, also when decode
+    launches follow one another back to back"""
+    lens = [777, 16, 4100, 0, 95, 2048]
+    c = build_decode_case(2300, lens, 8, 4, 128, 16)
+    ref = oracle_decode(c)
+    K.set_option(K.OPT_EARLY_METADATA, 0)
+    out0, ws = gpu_decode(c)
+    torch.cuda.synchronize()
+    try:
+        K.set_option(K.OPT_EARLY_METADATA, 1)
+        outs = []
+        for _ in range(4):                                       # back to back: launch k + 1 overlaps the tail of launch k
+            o = torch.zeros_like(out0)
+            gpu_decode(c, out=o, ws=ws)
+            outs.append(o)
+        torch.cuda.synchronize()
+        assert K.workspace_status(ws) == 0
+        for o in outs:
+            assert torch.equal(o, out0)
+    finally:
+        K.set_option(K.OPT_EARLY_METADATA, 0)
+    assert_close(out0, ref)
+
+
 def test_long_context_split_and_combine():
     """64k tokens on one kv head pair: the sequence is cut over every partition and merged by the combine kernel"""
     c = build_decode_case(2200, [65536], 2, 8, 128, 16)
