@@ -119,6 +119,21 @@ __device__ __forceinline__ uint2 lds64(uint32_t a) {
   asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(a));
   return r;
 }
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 r;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(a));
+  return r;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t r;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(a));
+  return r;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+  uint32_t r;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(r) : "r"(a));
+  return r;
+}
 __device__ __forceinline__ uint32_t lds8(uint32_t a) {
   uint32_t r;
   asm volatile("ld.shared.u8 %0, [%1];" : "=r"(r) : "r"(a));
@@ -165,6 +180,13 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t x) {
   uint32_t r;
   asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"((unsigned short)x));
   return r;
+}
+// four E4M3 bytes -> two f16x2 (bytes 0, 1 and bytes 2, 3)
+__device__ __forceinline__ void e4m3x4_to_f16x2(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+      : "=r"(lo), "=r"(hi)
+      : "r"(w));
 }
 __device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
   uint32_t r;

@@ -30,7 +30,10 @@
 
 namespace hkv {
 
-constexpr int TG = 4;            // consumer warps per CTA
+#ifndef HKV_TG
+#define HKV_TG 4
+#endif
+constexpr int TG = HKV_TG;       // consumer warps per CTA
 constexpr int NTHREADS = TG * 32;
 constexpr int RPAD = 8;          // query rows per (request, kv head) padded to the mma N tile
 constexpr float NEG_BIG = -1.0e30f;
@@ -86,11 +89,16 @@ struct Geo {
 #define HKV_NCH128 1
 #endif
   static constexpr int NCH = UB == 1 ? 2 : HKV_NCH128; // independent accumulators per score tile
-  // token (row of a 16-token block) handled by row i of the 16-row score tile (chosen so that the value loads of a
-  // warp hit distinct shared-memory banks)
-  __device__ static constexpr int tok(int i) { return (D == 128 && LAYOUT == 0) ? 2 * (i & 7) + (i >> 3) : i; }
-  // 16-channel block of a key row held by lane column c as its u-th block
-  __device__ static constexpr int kblk(int c, int u) { return D == 128 ? c + 4 * u : 2 * c + (u & 1) + 8 * (u >> 1); }
+  // token (row of a 16-token block) handled by row i of the 16-row score tile. With 72-byte rows (head_dim 128, slot
+  // layout) bits 1 and 3 of i are swapped: then the key loads of a half warp (rows i = 4k .. 4k+3, 16 bytes apart
+  // inside a row) and its value loads (rows i = j, j+2, j+4, j+6, 32 contiguous bytes of each) both touch every
+  // shared-memory bank once. 144-byte rows need no permutation.
+  __device__ static constexpr int tok(int i) {
+    return (D == 128 && LAYOUT == 0) ? ((i & 5) | ((i & 2) << 2) | ((i & 8) >> 2)) : i;
+  }
+  // 16-channel block of a key row held by lane column c as its u-th block: NBL adjacent blocks per lane, so that
+  // their scale bytes come with one load
+  __device__ static constexpr int kblk(int c, int u) { return NBL * c + u; }
 };
 
 // one request as the unit stream sees it; all fields are warp-uniform
@@ -265,9 +273,9 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   uint32_t koff_d = r0 * Gm::ROW + 8 * Gm::kblk(c, 0), koff_s = Gm::SF_BASE + r0 * Gm::SF_ROW + Gm::kblk(c, 0);
   uint32_t voff_d = Gm::TILE + t00 * Gm::ROW + 8 * g, voff_s = Gm::TILE + Gm::SF_BASE + t00 * Gm::SF_ROW + g;
   asm volatile("" : "+r"(ring_a), "+r"(bars_a), "+r"(koff_d), "+r"(koff_s), "+r"(voff_d), "+r"(voff_s));
-  constexpr int KR1 = (D == 128 && LAYOUT == 0) ? 1 : 8;                  // r1 - r0
-  constexpr int VR01 = (D == 128 && LAYOUT == 0) ? 2 : 1, VR10 = (D == 128 && LAYOUT == 0) ? 1 : 8,
-                VR11 = (D == 128 && LAYOUT == 0) ? 3 : 9;                 // t01 - t00, t10 - t00, t11 - t00
+  constexpr int KR1 = Gm::tok(8) - Gm::tok(0);                            // r1 - r0 (the same for every g)
+  constexpr int VR01 = Gm::tok(1) - Gm::tok(0), VR10 = Gm::tok(8) - Gm::tok(0),
+                VR11 = Gm::tok(9) - Gm::tok(0);                           // t01 - t00, t10 - t00, t11 - t00 (for every c)
 
   int f_b = cw.b, f_h = cw.h, f_U = cw.r.U, f_L = cw.r.L;
   int f_blk = w + (int)(lo - cw.seq0);              // unit (inside the cursor's sequence) to fetch next; may run past
@@ -463,20 +471,39 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
           float sa[Gm::NCH][4];
 #pragma unroll
           for (int i = 0; i < Gm::NCH; ++i) sa[i][0] = sa[i][1] = sa[i][2] = sa[i][3] = 0.0f;
+          // codes and scales of this lane's NBL adjacent key blocks of rows r0 and r1
+          const int dk = bi * 16 * Gm::ROW, sk = bi * 16 * Gm::SF_ROW;
+          uint2 w0[Gm::NBL], w1[Gm::NBL];
+          uint32_t h0[Gm::NBL / 2 + 1], h1[Gm::NBL / 2 + 1];   // f16x2 scale pairs (block 2j, block 2j+1) of r0 / r1
+          if (Gm::NBL == 2) {
+            w0[0] = lds64(kd_ + dk);
+            w0[1] = lds64(kd_ + dk + 8);
+            w1[0] = lds64(kd_ + dk + KR1 * Gm::ROW);
+            w1[1] = lds64(kd_ + dk + KR1 * Gm::ROW + 8);
+            h0[0] = e4m3x2_to_f16x2(lds16(ks_ + sk));
+            h1[0] = e4m3x2_to_f16x2(lds16(ks_ + sk + KR1 * Gm::SF_ROW));
+          } else {
+#pragma unroll
+            for (int j = 0; j < Gm::NBL / 2; ++j) {
+              const uint4 a = lds128(kd_ + dk + 16 * j), b = lds128(kd_ + dk + KR1 * Gm::ROW + 16 * j);
+              w0[2 * j] = make_uint2(a.x, a.y);
+              w0[2 * j + 1] = make_uint2(a.z, a.w);
+              w1[2 * j] = make_uint2(b.x, b.y);
+              w1[2 * j + 1] = make_uint2(b.z, b.w);
+            }
+            e4m3x4_to_f16x2(lds32(ks_ + sk), h0[0], h0[1]);
+            e4m3x4_to_f16x2(lds32(ks_ + sk + KR1 * Gm::SF_ROW), h1[0], h1[1]);
+          }
 #pragma unroll
           for (int u = 0; u < Gm::NBL; ++u) {
-            const int du = bi * 16 * Gm::ROW + 8 * (Gm::kblk(0, u) - Gm::kblk(0, 0));
-            const int su = bi * 16 * Gm::SF_ROW + Gm::kblk(0, u) - Gm::kblk(0, 0);
-            const uint2 w0 = lds64(kd_ + du);
-            const uint2 w1 = lds64(kd_ + du + KR1 * Gm::ROW);
-            const uint32_t f0 = lds8(ks_ + su), f1 = lds8(ks_ + su + KR1 * Gm::SF_ROW);
-            const __half2 sf = u32_as_h2(e4m3x2_to_f16x2(f0 | (f1 << 8)));   // (scale of row r0, scale of row r1)
-            const __half2 sf0 = __low2half2(sf), sf1 = __high2half2(sf);
+            const __half2 p0 = u32_as_h2(h0[u >> 1]), p1 = u32_as_h2(h1[u >> 1]);
+            const __half2 sf0 = (u & 1) ? __high2half2(p0) : __low2half2(p0);
+            const __half2 sf1 = (u & 1) ? __high2half2(p1) : __low2half2(p1);
             uint32_t e0[4], e1[4], e2[4], e3[4];
-            e2m1x8_to_f16x2(w0.x, e0);
-            e2m1x8_to_f16x2(w0.y, e1);
-            e2m1x8_to_f16x2(w1.x, e2);
-            e2m1x8_to_f16x2(w1.y, e3);
+            e2m1x8_to_f16x2(w0[u].x, e0);
+            e2m1x8_to_f16x2(w0[u].y, e1);
+            e2m1x8_to_f16x2(w1[u].x, e2);
+            e2m1x8_to_f16x2(w1[u].y, e3);
             // k-step v of this block: A = {row r0 k-low, row r1 k-low, row r0 k-high, row r1 k-high}
             mma_f16(sa[0], hmul2h(e0[0], sf0), hmul2h(e2[0], sf1), hmul2h(e0[1], sf0), hmul2h(e2[1], sf1),
                     qa[4 * u + 0][0], qa[4 * u + 0][1]);

@@ -54,10 +54,12 @@ class Geo:
         self.KS, self.NBL, self.NH = D // 16, D // 64, D // 128
 
     def tok(self, i):
-        return 2 * (i & 7) + (i >> 3) if (self.D == 128 and self.layout == 0) else i
+        if self.D == 128 and self.layout == 0:
+            return (i & 5) | ((i & 2) << 2) | ((i & 8) >> 2)       # bits 1 and 3 swapped
+        return i
 
     def kblk(self, c, u):
-        return c + 4 * u if self.D == 128 else 2 * c + (u & 1) + 8 * (u >> 1)
+        return self.NBL * c + u
 
 
 def movmatrix_trans(regs):
@@ -178,16 +180,47 @@ def test_negative_controls(wrong):
     assert err > 0.05
 
 
-def test_value_loads_hit_distinct_banks():
-    """the 64-bit value loads of a half warp (lanes 0-15) touch 32 distinct 4-byte banks in the slot layout"""
+def _wavefronts(addrs, width):
+    """shared-memory passes of one warp-wide load: 4-byte banks, a pass serves every lane whose words do not collide;
+    8-byte loads are served per half warp and 16-byte loads per quarter warp"""
+    group = {1: 32, 2: 32, 4: 32, 8: 16, 16: 8}[width]
+    total = 0
+    for s0 in range(0, 32, group):
+        words = {}
+        for a in addrs[s0:s0 + group]:
+            for wd in range(a // 4, (a + width + 3) // 4):
+                words.setdefault(wd % 32, set()).add(wd)
+        total += max(len(v) for v in words.values())
+    return total
+
+
+@pytest.mark.parametrize("D", [128, 256])
+def test_shared_memory_loads_are_conflict_free(D):
+    """every load pattern of the slot layout (key codes and scales, value codes and scales) takes the minimum number
+    of shared-memory passes"""
+    geo = Geo(D, 0)
+    lanes = [(lane >> 2, lane & 3) for lane in range(32)]
+    for row in (0, 8):
+        if D == 128:
+            for u in range(2):
+                assert _wavefronts([geo.tok(g + row) * geo.ROW + 8 * geo.kblk(c, u) for g, c in lanes], 8) == 2
+            assert _wavefronts([geo.SF_BASE + geo.tok(g + row) * geo.SF_ROW + geo.kblk(c, 0) for g, c in lanes], 2) == 1
+        else:
+            for j in range(2):
+                assert _wavefronts([geo.tok(g + row) * geo.ROW + 8 * geo.kblk(c, 0) + 16 * j for g, c in lanes], 16) == 4
+            assert _wavefronts([geo.SF_BASE + geo.tok(g + row) * geo.SF_ROW + geo.kblk(c, 0) for g, c in lanes], 4) == 1
+    for hf in range(geo.NH):
+        for off in (0, 1, 8, 9):
+            assert _wavefronts([geo.tok(2 * c + off) * geo.ROW + 8 * g + 64 * hf for g, c in lanes], 8) == 2
+            assert _wavefronts([geo.SF_BASE + geo.tok(2 * c + off) * geo.SF_ROW + g + 8 * hf for g, c in lanes], 1) == 1
+
+
+def test_row_offsets_are_lane_independent():
+    """the kernel addresses a lane's second key row and its other three value rows by constants"""
     for D in (128, 256):
-        geo = Geo(D, 0)
-        for which in range(4):
-            for half in range(2):
-                banks = []
-                for lane in range(16 * half, 16 * half + 16):
-                    g, c = lane >> 2, lane & 3
-                    t = (geo.tok(2 * c), geo.tok(2 * c + 1), geo.tok(2 * c + 8), geo.tok(2 * c + 9))[which]
-                    addr = t * geo.ROW + 8 * g
-                    banks += [(addr // 4) % 32, (addr // 4 + 1) % 32]
-                assert len(set(banks)) == 32, (D, which, half)
+        for layout in (0, 1):
+            geo = Geo(D, layout)
+            assert len({geo.tok(g + 8) - geo.tok(g) for g in range(8)}) == 1
+            for off in (1, 8, 9):
+                assert len({geo.tok(2 * c + off) - geo.tok(2 * c) for c in range(4)}) == 1
+            assert sorted(geo.tok(i) for i in range(16)) == list(range(16))
