@@ -68,12 +68,16 @@ __device__ __forceinline__ float block_sse(const float (&ax)[16], float s) {
 }
 
 // ---- division-free fast path -------------------------------------------------------------------------------------
-// The reference rounds y = RN(ax / s) onto the E2M1 grid. Here y is approximated by ax * RN(1 / s) (relative error
-// below 2^-22) and the hardware conversion cvt.rn.satfinite.e2m1x2.f32 (identical to the reference's threshold chain
-// for every non-negative fp32 input) is applied to y * (1 + 2^-20) and y * (1 - 2^-20) at once. The conversion is
-// monotone and RN(ax / s) lies between the two arguments, so equal codes prove the code of the exact quotient; a
-// block with any unequal pair, or a scale outside [2^-96, 2^96], is redone with IEEE divisions. The error terms
-// (code * s - ax)^2 are still single IEEE operations in the reference's order.
+// The reference rounds y = RN(ax / s) onto the E2M1 grid. Here the quotient is bracketed by ax * RN(r * (1 + 2^-20))
+// and ax * RN(r * (1 - 2^-20)), r = RN(1 / s) (three roundings of relative error 2^-24 each, far inside the 2^-20
+// band), and the hardware conversion cvt.rn.satfinite.e2m1x2.f32 (identical to the reference's threshold chain for
+// every non-negative fp32 input) is applied to both at once. The conversion is monotone and RN(ax / s) lies between
+// the two arguments, so equal codes prove the code of the exact quotient. Unequal codes k, k + 1 mean the quotient is
+// within 2^-20 of the threshold t between them, often exactly on it when the global scale has few mantissa bits. That
+// case is decided exactly without a division: every threshold has an even mantissa, so RN(q) <= t holds iff
+// q <= t + ulp/2 and RN(q) < t iff q < t - ulp'/2 (ulp' of the binade below), and q <= m is ax <= m * s, a product
+// of a 26-bit and a 24-bit significand that fp64 holds exactly. A scale outside [2^-96, 2^96] takes the IEEE-division
+// path. The error terms (code * s - ax)^2 are still single IEEE operations in the reference's order.
 __device__ __forceinline__ unsigned e2m1_pair(float hi, float lo) {      // code(hi) in bits 7:4, code(lo) in bits 3:0
   unsigned short r;
   asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; mov.b16 %0, {t, 0}; }" : "=h"(r) : "f"(hi), "f"(lo));
@@ -87,15 +91,29 @@ __device__ __forceinline__ float e2m1_pair_value(unsigned b) {           // valu
 constexpr float kUp = 1.0f + 9.5367431640625e-07f, kDown = 1.0f - 9.5367431640625e-07f;   // 1 +- 2^-20
 __device__ __forceinline__ bool fast_scale_ok(float s) { return s >= 1.2621774e-29f && s <= 7.9228163e28f; }
 
-// squared error of the block under scale s with reciprocal r; `risk` collects code disagreements (bits 3:0)
-__device__ __forceinline__ float block_sse_fast(const float (&ax)[16], float s, float r, unsigned& risk) {
+// rounding boundary of the quotient between E2M1 magnitude codes k and k + 1: t + ulp(t) / 2 for the "<=" thresholds
+// 0.25, 1.25, 2.5, 5 (k even), t - ulp(pred t) / 2 for the "<" thresholds 0.75, 1.75, 3.5 (k odd)
+__constant__ double kBoundary[8] = {0.25 + 0x1p-26, 0.75 - 0x1p-25, 1.25 + 0x1p-24, 1.75 - 0x1p-24,
+                                    2.5 + 0x1p-23,  3.5 - 0x1p-23,  5.0 + 0x1p-22,  0.0};
+// exact magnitude code of RN(ax / s) when the bracket gave codes k and k + 1 (rare; never inlined into the hot loop)
+static __device__ __noinline__ unsigned resolve_code(float ax, float s, unsigned k) {
+  const double lhs = (double)ax, rhs = kBoundary[k & 7u] * (double)s;
+  return ((k & 1u) ? lhs < rhs : lhs <= rhs) ? k : k + 1u;
+}
+// magnitude code of RN(ax / s) from the bracket (ax * r_up, ax * r_down)
+__device__ __forceinline__ unsigned fast_code(float ax, float s, float r_up, float r_down) {
+  const unsigned b = e2m1_pair(ax * r_up, ax * r_down);
+  unsigned k = b & 7u;
+  if (((b >> 4) ^ b) & 7u) k = resolve_code(ax, s, k);
+  return k;
+}
+
+// squared error of the block under scale s with bracketing reciprocals r_up, r_down
+__device__ __forceinline__ float block_sse_fast(const float (&ax)[16], float s, float r_up, float r_down) {
   float acc = 0.0f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    const float y = ax[i] * r;
-    const unsigned b = e2m1_pair(y * kUp, y * kDown);
-    risk |= b ^ (b >> 4);
-    const float d = __fsub_rn(__fmul_rn(e2m1_pair_value(b), s), ax[i]);
+    const float d = __fsub_rn(__fmul_rn(e2m1_pair_value(fast_code(ax[i], s, r_up, r_down)), s), ax[i]);
     const float sq = __fmul_rn(d, d);
     acc = i == 0 ? sq : __fadd_rn(acc, sq);
   }
@@ -151,10 +169,12 @@ __global__ void __launch_bounds__(1024) write_kernel(const WriteParams p) {
                  : (int)e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 4.0f)));
     const float sc = __fmul_rn(e4m3_dec((unsigned)cc), g);
     float err;
-    unsigned risk = fast_scale_ok(sc) ? 0u : 15u;
-    if (risk == 0u) err = block_sse_fast(ax, sc, __frcp_rn(sc), risk);
-    if (risk & 15u) err = block_sse(ax, sc);          // rare: a quotient too close to a rounding boundary, or a
-                                                      // zero / extreme scale
+    if (fast_scale_ok(sc)) {
+      const float r = __frcp_rn(sc);
+      err = block_sse_fast(ax, sc, r * kUp, r * kDown);
+    } else {
+      err = block_sse(ax, sc);                        // rare: a zero or extreme scale
+    }
     const int lane0 = (threadIdx.x & 31) & ~3;
     float best = __shfl_sync(0xffffffffu, err, lane0);
     cb = __shfl_sync(0xffffffffu, cc, lane0);
@@ -175,16 +195,13 @@ __global__ void __launch_bounds__(1024) write_kernel(const WriteParams p) {
   const float x0 = __uint_as_float(wa << 16), x1 = __uint_as_float(wa & 0xffff0000u);
   const float x2 = __uint_as_float(wb << 16), x3 = __uint_as_float(wb & 0xffff0000u);
   unsigned m0, m1, m2, m3;
-  unsigned risk = fast_scale_ok(s) ? 0u : 15u;
-  if (risk == 0u) {
-    const float r = __frcp_rn(s);
-    const float y0 = fabsf(x0) * r, y1 = fabsf(x1) * r, y2 = fabsf(x2) * r, y3 = fabsf(x3) * r;
-    const unsigned b0 = e2m1_pair(y0 * kUp, y0 * kDown), b1 = e2m1_pair(y1 * kUp, y1 * kDown);
-    const unsigned b2 = e2m1_pair(y2 * kUp, y2 * kDown), b3 = e2m1_pair(y3 * kUp, y3 * kDown);
-    risk = (b0 ^ (b0 >> 4)) | (b1 ^ (b1 >> 4)) | (b2 ^ (b2 >> 4)) | (b3 ^ (b3 >> 4));
-    m0 = b0 & 7u; m1 = b1 & 7u; m2 = b2 & 7u; m3 = b3 & 7u;
-  }
-  if (risk & 15u) {
+  if (fast_scale_ok(s)) {
+    const float r = __frcp_rn(s), r_up = r * kUp, r_down = r * kDown;
+    m0 = fast_code(fabsf(x0), s, r_up, r_down);
+    m1 = fast_code(fabsf(x1), s, r_up, r_down);
+    m2 = fast_code(fabsf(x2), s, r_up, r_down);
+    m3 = fast_code(fabsf(x3), s, r_up, r_down);
+  } else {
     m0 = mag_of(fabsf(x0), s); m1 = mag_of(fabsf(x1), s); m2 = mag_of(fabsf(x2), s); m3 = mag_of(fabsf(x3), s);
   }
   const uint32_t code = (m0 | (x0 < 0.0f ? 8u : 0u)) | ((m1 | (x1 < 0.0f ? 8u : 0u)) << 4) |
