@@ -1,9 +1,10 @@
 // Quantize-on-write for the NVFP4 paged KV cache (sm_100a).
 //
-// Four threads own one block of 16 consecutive channels of one (token, kv head, side): they read its 32 bytes of
-// bf16, pick the E4M3 block scale (optionally by the 4-candidate squared-error search, one candidate per thread),
-// encode the 16 E2M1 codes and store 8 code bytes + 1 scale byte at slot = page * PS + position. Consecutive quads cover
-// consecutive blocks, so a warp reads 256 contiguous bytes and stores 64 contiguous code bytes.
+// A block of 16 consecutive channels of one (token, kv head, side) is 32 bytes of bf16 in and 8 code bytes + 1 scale
+// byte out, stored at slot = page * PS + position. The E4M3 block scale is picked (optionally) by the reference's
+// 4-candidate squared-error search. Large launches give every block to one lane, which scores the candidates in turn;
+// small launches (decode appends) give it to a quad, one candidate per lane. The 16 magnitude codes of a candidate
+// live in two registers (a nibble each), produced eight at a time by the hardware E2M1 conversion.
 //
 // Bit-exactness: the result must equal the reference's PyTorch quantiser (kv_fp4_ref.py:159-186 `quantize_rows`,
 // rules at kv_fp4_ref.py:15-25) byte for byte. Every arithmetic step is therefore a single IEEE fp32 operation issued
@@ -49,23 +50,7 @@ __device__ __forceinline__ unsigned e2m1_mag(float y) {
   return y <= 0.25f ? 0u : y < 0.75f ? 1u : y <= 1.25f ? 2u : y < 1.75f ? 3u : y <= 2.5f ? 4u : y < 3.5f ? 5u
        : y <= 5.0f ? 6u : 7u;
 }
-__device__ __forceinline__ float e2m1_val(unsigned m) {
-  const unsigned e = (m >> 1) & 3u, l = m & 1u;
-  return e ? __uint_as_float(((e + 126u) << 23) | (l << 22)) : (l ? 0.5f : 0.0f);
-}
 __device__ __forceinline__ unsigned mag_of(float ax, float s) { return s > 0.0f ? e2m1_mag(__fdiv_rn(ax, s)) : 0u; }
-
-// sequential squared error of the block under effective scale s (kv_fp4_ref.py:148-156)
-__device__ __forceinline__ float block_sse(const float (&ax)[16], float s) {
-  float acc = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float d = __fsub_rn(__fmul_rn(e2m1_val(mag_of(ax[i], s)), s), ax[i]);
-    const float sq = __fmul_rn(d, d);
-    acc = i == 0 ? sq : __fadd_rn(acc, sq);
-  }
-  return acc;
-}
 
 // ---- division-free fast path -------------------------------------------------------------------------------------
 // The reference rounds y = RN(ax / s) onto the E2M1 grid. Here the quotient is bracketed by ax * RN(r * (1 + 2^-20))
@@ -78,16 +63,6 @@ __device__ __forceinline__ float block_sse(const float (&ax)[16], float s) {
 // q <= t + ulp/2 and RN(q) < t iff q < t - ulp'/2 (ulp' of the binade below), and q <= m is ax <= m * s, a product
 // of a 26-bit and a 24-bit significand that fp64 holds exactly. A scale outside [2^-96, 2^96] takes the IEEE-division
 // path. The error terms (code * s - ax)^2 are still single IEEE operations in the reference's order.
-__device__ __forceinline__ unsigned e2m1_pair(float hi, float lo) {      // code(hi) in bits 7:4, code(lo) in bits 3:0
-  unsigned short r;
-  asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; mov.b16 %0, {t, 0}; }" : "=h"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-__device__ __forceinline__ float e2m1_pair_value(unsigned b) {           // value of the code in bits 3:0
-  unsigned h2;
-  asm("{ .reg .b8 t, z; mov.b16 {t, z}, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h2) : "h"((unsigned short)b));
-  return __half2float(__ushort_as_half((unsigned short)(h2 & 0xffffu)));
-}
 constexpr float kUp = 1.0f + 9.5367431640625e-07f, kDown = 1.0f - 9.5367431640625e-07f;   // 1 +- 2^-20
 __device__ __forceinline__ bool fast_scale_ok(float s) { return s >= 1.2621774e-29f && s <= 7.9228163e28f; }
 
@@ -100,51 +75,114 @@ static __device__ __noinline__ unsigned resolve_code(float ax, float s, unsigned
   const double lhs = (double)ax, rhs = kBoundary[k & 7u] * (double)s;
   return ((k & 1u) ? lhs < rhs : lhs <= rhs) ? k : k + 1u;
 }
-// magnitude code of RN(ax / s) from the bracket (ax * r_up, ax * r_down)
-__device__ __forceinline__ unsigned fast_code(float ax, float s, float r_up, float r_down) {
-  const unsigned b = e2m1_pair(ax * r_up, ax * r_down);
-  unsigned k = b & 7u;
-  if (((b >> 4) ^ b) & 7u) k = resolve_code(ax, s, k);
-  return k;
+// E2M1 magnitude codes of y0 .. y7 (all >= 0), value i in nibble i
+__device__ __forceinline__ uint32_t e2m1_codes8(float y0, float y1, float y2, float y3, float y4, float y5, float y6,
+                                                float y7) {
+  uint32_t w;
+  asm("{\n\t.reg .b8 t0, t1, t2, t3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n\t"
+      "mov.b32 %0, {t0, t1, t2, t3};\n\t}"
+      : "=r"(w)
+      : "f"(y0), "f"(y1), "f"(y2), "f"(y3), "f"(y4), "f"(y5), "f"(y6), "f"(y7));
+  return w;
+}
+__device__ __forceinline__ uint32_t bracket_codes8(const float (&ax)[16], int o, float r) {
+  return e2m1_codes8(ax[o] * r, ax[o + 1] * r, ax[o + 2] * r, ax[o + 3] * r, ax[o + 4] * r, ax[o + 5] * r,
+                     ax[o + 6] * r, ax[o + 7] * r);
 }
 
-// squared error of the block under scale s with bracketing reciprocals r_up, r_down
-__device__ __forceinline__ float block_sse_fast(const float (&ax)[16], float s, float r_up, float r_down) {
+// the 16 magnitude codes of a block under scale s: value i in nibble i % 8 of word i / 8
+struct BlockCodes {
+  uint32_t w[2];
+};
+__device__ __forceinline__ BlockCodes block_codes_fast(const float (&ax)[16], float s, float r) {
+  const float r_up = r * kUp, r_down = r * kDown;
+  BlockCodes c;
+  uint32_t diff[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    c.w[h] = bracket_codes8(ax, 8 * h, r_down);
+    diff[h] = c.w[h] ^ bracket_codes8(ax, 8 * h, r_up);
+  }
+  if (diff[0] | diff[1]) {                        // rare: some quotient lies within 2^-20 of a rounding boundary
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int sh = 4 * (i & 7);
+      if ((diff[i >> 3] >> sh) & 15u) {
+        const unsigned k = resolve_code(ax[i], s, (c.w[i >> 3] >> sh) & 7u);
+        c.w[i >> 3] = (c.w[i >> 3] & ~(15u << sh)) | (k << sh);
+      }
+    }
+  }
+  return c;
+}
+__device__ __forceinline__ BlockCodes block_codes_exact(const float (&ax)[16], float s) {   // IEEE divisions
+  BlockCodes c;
+  c.w[0] = c.w[1] = 0u;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) c.w[i >> 3] |= mag_of(ax[i], s) << (4 * (i & 7));
+  return c;
+}
+// sequential squared error of the block for given codes (kv_fp4_ref.py:148-156): single IEEE operations, i = 0..15
+__device__ __forceinline__ float codes_sse(const float (&ax)[16], const BlockCodes& c, float s) {
   float acc = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float d = __fsub_rn(__fmul_rn(e2m1_pair_value(fast_code(ax[i], s, r_up, r_down)), s), ax[i]);
-    const float sq = __fmul_rn(d, d);
-    acc = i == 0 ? sq : __fadd_rn(acc, sq);
+  for (int h = 0; h < 2; ++h) {
+    uint32_t v[4];                                // f16x2 values of the word's code pairs
+    e2m1x8_to_f16x2(c.w[h], v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half2 hv = u32_as_h2(v[j]);
+      const int i = 8 * h + 2 * j;
+      const float d0 = __fsub_rn(__fmul_rn(__low2float(hv), s), ax[i]);
+      const float q0 = __fmul_rn(d0, d0);
+      acc = i == 0 ? q0 : __fadd_rn(acc, q0);
+      const float d1 = __fsub_rn(__fmul_rn(__high2float(hv), s), ax[i + 1]);
+      acc = __fadd_rn(acc, __fmul_rn(d1, d1));
+    }
   }
   return acc;
 }
+__device__ __forceinline__ void score(const float (&ax)[16], float sc, BlockCodes& c, float& err, bool want_err) {
+  if (fast_scale_ok(sc)) c = block_codes_fast(ax, sc, __frcp_rn(sc));
+  else c = block_codes_exact(ax, sc);             // rare: a zero or extreme scale
+  if (want_err) err = codes_sse(ax, c, sc);
+}
 
-// Four lanes share one block of 16 values: every lane reads the whole block (the four identical 16-byte requests of
-// a quad are served by one access), lane k of the quad scores scale candidate k, the quad agrees on the winner with
-// shuffles in candidate order (strict "<", so the earliest candidate wins a tie, as in the reference), and every lane
-// encodes 4 of the 16 values. One CTA handles one token: 2 * KVH * D / 16 blocks spread over its quads.
-template <int D, int SEARCH>
-__global__ void __launch_bounds__(1024) write_kernel(const WriteParams p) {
+// LPB lanes own one block of 16 consecutive channels of one (token, kv head, side). LPB = 1 (prefill-sized launches):
+// the lane reads the block's 32 bytes, scores the four scale candidates one after the other, keeps the codes of the
+// best one and stores 8 code bytes and the scale byte: consecutive lanes cover consecutive blocks, so a warp reads 1 KB
+// and stores 256 B contiguous. LPB = 4 (few tokens, latency matters): the four lanes of a quad read the same block,
+// lane k scores candidate k, the quad agrees on the winner with shuffles in candidate order (strict "<", so the
+// earliest candidate wins a tie, as in the reference) and every lane stores 4 of the 16 codes.
+template <int D, int SEARCH, int LPB>
+__global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   constexpr int NB = D / 16;                      // blocks per row
   pdl_wait();                                     // inputs and the cache may come from the preceding launch
   pdl_launch_dependents();
-  // one CTA per token; its 2 * KVH * NB blocks are spread over the CTA's quads (all index math in 32 bits)
-  const long long t = blockIdx.x;
+  const int n_blocks = 2 * p.KVH * NB;            // per token (a multiple of 16)
+  const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LPB;
+  const int cand = LPB == 4 ? (threadIdx.x & 3) : 0;
+  const long long t = gid / n_blocks;
+  if (t >= p.n_slots) return;                     // whole quads (gid is shared by a quad), whole warps when LPB == 4
+  const int bid = (int)(gid - t * n_blocks);
   const long long slot = p.slots[t];
-  if (slot < 0) return;                           // uniform per CTA
-  long long page, pos;
-  if ((p.PS & (p.PS - 1)) == 0) {
-    const int sh = 31 - __clz(p.PS);
-    page = slot >> sh;
-    pos = slot & (p.PS - 1);
-  } else {
-    page = slot / p.PS;
-    pos = slot - page * p.PS;
+  // a quad shares its token, so `active` is uniform in a quad; inactive lanes still take part in the shuffles below
+  const bool active = slot >= 0;
+  long long page = 0, pos = 0;
+  if (active) {
+    if ((p.PS & (p.PS - 1)) == 0) {
+      const int sh = 31 - __clz(p.PS);
+      page = slot >> sh;
+      pos = slot & (p.PS - 1);
+    } else {
+      page = slot / p.PS;
+      pos = slot - page * p.PS;
+    }
   }
-  const int cand = threadIdx.x & 3;
-  const int n_blocks = 2 * p.KVH * NB;
-  for (int bid = threadIdx.x >> 2; bid < n_blocks; bid += blockDim.x >> 2) {   // n_blocks is a multiple of 16
   const int side = bid >= p.KVH * NB;
   const int hb = side ? bid - p.KVH * NB : bid;
   const int h = hb / NB, blk = hb - h * NB;
@@ -153,63 +191,76 @@ __global__ void __launch_bounds__(1024) write_kernel(const WriteParams p) {
   const uint4 w0 = *reinterpret_cast<const uint4*>(src + blk * 16);
   const uint4 w1 = *reinterpret_cast<const uint4*>(src + blk * 16 + 8);
   const uint32_t ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-  float ax[16];
+  float x[16], ax[16];
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    ax[2 * i] = fabsf(__uint_as_float(ws[i] << 16));
-    ax[2 * i + 1] = fabsf(__uint_as_float(ws[i] & 0xffff0000u));
+    x[2 * i] = __uint_as_float(ws[i] << 16);
+    x[2 * i + 1] = __uint_as_float(ws[i] & 0xffff0000u);
+    ax[2 * i] = fabsf(x[2 * i]);
+    ax[2 * i + 1] = fabsf(x[2 * i + 1]);
     amax = fmaxf(amax, fmaxf(ax[2 * i], ax[2 * i + 1]));
   }
   const float g = side ? p.gv[h] : p.gk[h];
   const int c0 = (int)e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 6.0f)));
   int cb = c0;
-  if (SEARCH) {
-    const int cc = cand == 0 ? c0 : cand == 1 ? min(c0 + 1, 126) : cand == 2 ? max(c0 - 1, 0)
-                 : (int)e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 4.0f)));
-    const float sc = __fmul_rn(e4m3_dec((unsigned)cc), g);
-    float err;
-    if (fast_scale_ok(sc)) {
-      const float r = __frcp_rn(sc);
-      err = block_sse_fast(ax, sc, r * kUp, r * kDown);
-    } else {
-      err = block_sse(ax, sc);                        // rare: a zero or extreme scale
-    }
-    const int lane0 = (threadIdx.x & 31) & ~3;
-    float best = __shfl_sync(0xffffffffu, err, lane0);
-    cb = __shfl_sync(0xffffffffu, cc, lane0);
-#pragma unroll
-    for (int k = 1; k < 4; ++k) {
-      const float ek = __shfl_sync(0xffffffffu, err, lane0 + k);
-      const int ck = __shfl_sync(0xffffffffu, cc, lane0 + k);
-      if (ek < best) {
-        best = ek;
-        cb = ck;
-      }
-    }
-  }
-  const float s = __fmul_rn(e4m3_dec((unsigned)cb), g);
-  // this lane's 4 values: elements 4 cand .. 4 cand + 3 (two bf16 pairs), sign from "x < 0" (false for -0.0)
-  const uint32_t wa = cand == 0 ? ws[0] : cand == 1 ? ws[2] : cand == 2 ? ws[4] : ws[6];
-  const uint32_t wb = cand == 0 ? ws[1] : cand == 1 ? ws[3] : cand == 2 ? ws[5] : ws[7];
-  const float x0 = __uint_as_float(wa << 16), x1 = __uint_as_float(wa & 0xffff0000u);
-  const float x2 = __uint_as_float(wb << 16), x3 = __uint_as_float(wb & 0xffff0000u);
-  unsigned m0, m1, m2, m3;
-  if (fast_scale_ok(s)) {
-    const float r = __frcp_rn(s), r_up = r * kUp, r_down = r * kDown;
-    m0 = fast_code(fabsf(x0), s, r_up, r_down);
-    m1 = fast_code(fabsf(x1), s, r_up, r_down);
-    m2 = fast_code(fabsf(x2), s, r_up, r_down);
-    m3 = fast_code(fabsf(x3), s, r_up, r_down);
+  BlockCodes best;
+  if (!SEARCH) {
+    float unused;
+    score(ax, __fmul_rn(e4m3_dec((unsigned)c0), g), best, unused, false);
   } else {
-    m0 = mag_of(fabsf(x0), s); m1 = mag_of(fabsf(x1), s); m2 = mag_of(fabsf(x2), s); m3 = mag_of(fabsf(x3), s);
+    const int c3 = (int)e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 4.0f)));
+    if (LPB == 1) {
+      float best_err = 0.0f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int cc = k == 0 ? c0 : k == 1 ? min(c0 + 1, 126) : k == 2 ? max(c0 - 1, 0) : c3;
+        BlockCodes c;
+        float err;
+        score(ax, __fmul_rn(e4m3_dec((unsigned)cc), g), c, err, true);
+        if (k == 0 || err < best_err) {
+          best_err = err;
+          best = c;
+          cb = cc;
+        }
+      }
+    } else {
+      const int cc = cand == 0 ? c0 : cand == 1 ? min(c0 + 1, 126) : cand == 2 ? max(c0 - 1, 0) : c3;
+      BlockCodes c;
+      float err;
+      score(ax, __fmul_rn(e4m3_dec((unsigned)cc), g), c, err, true);
+      const int lane0 = (threadIdx.x & 31) & ~3;
+      float best_err = __shfl_sync(0xffffffffu, err, lane0);
+      int win = 0;
+      cb = __shfl_sync(0xffffffffu, cc, lane0);
+#pragma unroll
+      for (int k = 1; k < 4; ++k) {
+        const float ek = __shfl_sync(0xffffffffu, err, lane0 + k);
+        const int ck = __shfl_sync(0xffffffffu, cc, lane0 + k);
+        if (ek < best_err) {
+          best_err = ek;
+          cb = ck;
+          win = k;
+        }
+      }
+      best.w[0] = __shfl_sync(0xffffffffu, c.w[0], lane0 + win);
+      best.w[1] = __shfl_sync(0xffffffffu, c.w[1], lane0 + win);
+    }
   }
-  const uint32_t code = (m0 | (x0 < 0.0f ? 8u : 0u)) | ((m1 | (x1 < 0.0f ? 8u : 0u)) << 4) |
-                        ((m2 | (x2 < 0.0f ? 8u : 0u)) << 8) | ((m3 | (x3 < 0.0f ? 8u : 0u)) << 12);
-  uint8_t* dd = (side ? p.vd : p.kd) + page * p.dsp + pos * p.dst + h * p.dsh + blk * 8 + 2 * cand;
-  *reinterpret_cast<uint16_t*>(dd) = (uint16_t)code;
+  if (!active) return;
+  // sign bit of every code from "x < 0" (false for -0.0 and NaN, as in the reference)
+  uint32_t sg[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 16; ++i) sg[i >> 3] |= x[i] < 0.0f ? (8u << (4 * (i & 7))) : 0u;
+  const uint32_t lo = best.w[0] | sg[0], hi = best.w[1] | sg[1];
+  uint8_t* dd = (side ? p.vd : p.kd) + page * p.dsp + pos * p.dst + h * p.dsh + blk * 8;
+  if (LPB == 1) {
+    *reinterpret_cast<uint2*>(dd) = make_uint2(lo, hi);
+  } else {
+    const uint32_t wsel = cand < 2 ? lo : hi;
+    *reinterpret_cast<uint16_t*>(dd + 2 * cand) = (uint16_t)(cand & 1 ? wsel >> 16 : wsel);
+  }
   if (cand == 0) (side ? p.vsf : p.ksf)[page * p.ssp + pos * p.sst + h * p.ssh + blk] = (uint8_t)cb;
-  }
 }
 
 static int g_last_cuda_error = 0;
@@ -271,14 +322,20 @@ extern "C" int hkv_write(const void* key, const void* val, int64_t ks0, int64_t 
   p.slots = (const long long*)slots;
   p.n_slots = n_slots;
   p.gk = gk; p.gv = gv; p.PS = PS; p.KVH = KVH;
-  const long long blocks = n_slots;                 // one CTA per token
+  // lanes: one per (token, block) for prefill-sized launches, a quad per (token, block) for few tokens (decode appends)
+  const int lpb = n_slots <= 4096 ? 4 : 1;
+  const int threads = 256;
+  const long long lanes = n_slots * (2ll * KVH * (D / 16)) * lpb;
+  const long long blocks = (lanes + threads - 1) / threads;
   if (blocks > 0x7fffffffll) return HKV_ERR_RANGE;
   cudaStream_t st = (cudaStream_t)stream;
-  void (*k)(const WriteParams) = D == 128 ? (search ? write_kernel<128, 1> : write_kernel<128, 0>)
-                                          : (search ? write_kernel<256, 1> : write_kernel<256, 0>);
-  // few tokens (decode appends): one quad per block so that a token's blocks are quantised side by side; many tokens
-  // (prefill): 256 threads per CTA loop over the token's blocks
-  int threads = 256;
-  if (n_slots <= 4096) threads = std::min(1024, std::max(128, 2 * KVH * (D / 16) * 4));
+  void (*k)(const WriteParams);
+  if (D == 128) {
+    k = lpb == 1 ? (search ? write_kernel<128, 1, 1> : write_kernel<128, 0, 1>)
+                 : (search ? write_kernel<128, 1, 4> : write_kernel<128, 0, 4>);
+  } else {
+    k = lpb == 1 ? (search ? write_kernel<256, 1, 1> : write_kernel<256, 0, 1>)
+                 : (search ? write_kernel<256, 1, 4> : write_kernel<256, 0, 4>);
+  }
   return record_cuda(launch_pdl(k, dim3((unsigned)blocks), dim3(threads), 0, st, p));
 }
