@@ -25,7 +25,7 @@ from .layout import flat_views, slot_bytes, slot_views
 
 HEAD_SIZES = (128, 256)
 PAGE_SIZES = (16, 32, 64)
-MAX_ROWS = 8                      # query rows per kv head the decode kernel holds: G * (1 + draft tokens) <= 8
+MAX_ROWS = 64                     # query rows per kv head, G * (1 + draft tokens): eight per pass over the cache
 _STATE = {}                       # per device: decode workspace
 
 

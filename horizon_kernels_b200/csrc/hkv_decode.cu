@@ -35,7 +35,8 @@ namespace hkv {
 #endif
 constexpr int TG = HKV_TG;       // consumer warps per CTA
 constexpr int NTHREADS = TG * 32;
-constexpr int RPAD = 8;          // query rows per (request, kv head) padded to the mma N tile
+constexpr int RPAD = 8;          // query rows per (request, kv head) of one pass, padded to the mma N tile
+constexpr int kMaxRows = 64;     // G * qlmax: more than RPAD rows are served by several passes over the cache
 constexpr float NEG_BIG = -1.0e30f;
 constexpr float TAU = 8.0f;      // lazy rescale threshold (log2 domain): P stays below 2^8, inside f16's range
 
@@ -55,6 +56,7 @@ struct DecodeParams {
   uint8_t* ws;
   __nv_bfloat16* out;
   int MP, B, KVH, G, qlmax, PS;
+  int row0;                                          // first query row (of the G * ql rows of a request and kv head) of this pass
   int early_meta;                                    // seq_lens / query_start_loc are read before the launch dependency
   float scale_log2, v_scale;
 };
@@ -110,7 +112,7 @@ __device__ __forceinline__ ReqInfo load_req(const DecodeParams& p, int b) {
   ReqInfo r;
   r.q0 = __ldg(p.qsl + b);
   int ql = __ldg(p.qsl + b + 1) - r.q0;
-  ql = (ql < 0 || ql > p.qlmax) ? 0 : ql;
+  ql = (ql < 0 || ql > p.qlmax || p.G * ql <= p.row0) ? 0 : ql;     // (no rows in this pass: the request is skipped)
   r.ql = ql;
   r.L = ql > 0 ? max(__ldg(p.seq_lens + b), 0) : 0;
   r.U = ql > 0 ? max(1, (r.L + (1 << LOG_UT) - 1) >> LOG_UT) : 0;
@@ -391,7 +393,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
     const int n_piece = (int)(piece_end - pos);
     const int k0 = (int)(pos - lo);                 // partition-local index of the piece's first unit
     const int b = cw.b, h = cw.h, L = cw.r.L, ql = cw.r.ql, q0 = cw.r.q0, G = p.G;
-    const int R = G * ql;
+    const int R = min(RPAD, G * ql - p.row0);      // query rows of this pass: rows row0 .. row0 + R - 1 of the group
     const bool complete = blk0 == 0 && piece_end == seq_end;
     if (piece_idx == 0 && tid == 0) {
       PartDesc d;
@@ -420,7 +422,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       uint32_t qa[Gm::KS][2];
       {
         const bool have = g < R;
-        const int t = have ? g / G : 0, gq = have ? g - t * G : 0;
+        const int t = have ? (p.row0 + g) / G : 0, gq = have ? p.row0 + g - t * G : 0;
         const __nv_bfloat16* qrow = p.q + ((long long)(q0 + t) * (KVH * G) + h * G + gq) * D;
 #pragma unroll
         for (int u = 0; u < Gm::NBL; ++u) {
@@ -442,8 +444,9 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
         }
       }
       // visible context of query rows 2c, 2c+1 (causal among the request's own query tokens)
-      const int lim0 = 2 * c < R ? L - ql + (2 * c) / G + 1 : L, lim1 = 2 * c + 1 < R ? L - ql + (2 * c + 1) / G + 1 : L;
-      const int blk_mask = (L - ql + 1) >> LOG_UT;   // units below this one are visible to every query row in full
+      const int lim0 = 2 * c < R ? L - ql + (p.row0 + 2 * c) / G + 1 : L,
+                lim1 = 2 * c + 1 < R ? L - ql + (p.row0 + 2 * c + 1) / G + 1 : L;
+      const int blk_mask = (L - ql + p.row0 / G + 1) >> LOG_UT;   // units below this one are visible to every row in full
       float mneg0 = -m0 * sc, mneg1 = -m1 * sc;      // p = 2^(s * sc + mneg)
       float thr0 = m0 + tau_raw, thr1 = m1 + tau_raw;
 
@@ -684,7 +687,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
         }
         const float inv = den > 0.0f ? gvh / den : 0.0f;
         if (complete) {
-          const int t = row / G, gq = row - t * G;
+          const int t = (p.row0 + row) / G, gq = p.row0 + row - t * G;
           __nv_bfloat16* dst = p.out + ((long long)(q0 + t) * (KVH * G) + h * G + gq) * D + ch;
           *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(n0 * inv * p.v_scale, n1 * inv * p.v_scale);
         } else {
@@ -714,7 +717,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
 // between, and slot 0 of this one. Weights w_i = 2^(lse_i - max) / sum, summed in partition order.
 template <int D>
 __global__ void __launch_bounds__(128) combine_kernel(const uint8_t* ws, const int* qsl, __nv_bfloat16* out, int KVH,
-                                                      int G, int qlmax, float v_scale) {
+                                                      int G, int qlmax, int row0, float v_scale) {
   const int part = blockIdx.x, tid = threadIdx.x;
   pdl_wait();                                     // the workspace is written by the preceding decode launch
   pdl_launch_dependents();
@@ -729,11 +732,11 @@ __global__ void __launch_bounds__(128) combine_kernel(const uint8_t* ws, const i
   const int q0 = qsl[d.b];
   int ql = qsl[d.b + 1] - q0;
   ql = (ql < 0 || ql > qlmax) ? 0 : ql;
-  const int R = G * ql;
+  const int R = min(RPAD, G * ql - row0);           // rows row0 .. row0 + R - 1 of the group were computed by this pass
   const float ninf = -__int_as_float(0x7f800000);
   const int first = d.first_part, first_slot = d.first_slot;
   constexpr int GRP = 8;                            // pieces merged per round: their loads are independent
-  for (int idx = tid; idx < G * qlmax * (D / 2); idx += 128) {
+  for (int idx = tid; idx < R * (D / 2); idx += 128) {
     const int row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
     // a running maximum carries the log-sum-exp weights from round to round (fixed order => deterministic)
     float mx = ninf, tot = 0.0f, n0 = 0.0f, n1 = 0.0f;
@@ -765,9 +768,9 @@ __global__ void __launch_bounds__(128) combine_kernel(const uint8_t* ws, const i
         n1 += v[i].y * wgt;
       }
     }
-    if (row < R) {
+    {
       const float inv = tot > 0.0f ? v_scale / tot : 0.0f;
-      const int t = row / G, gq = row - t * G;
+      const int t = (row0 + row) / G, gq = row0 + row - t * G;
       __nv_bfloat16* dst = out + ((long long)(q0 + t) * (KVH * G) + d.h * G + gq) * D + ch;
       *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(n0 * inv, n1 * inv);
     }
@@ -822,7 +825,7 @@ static int max_parts(const DeviceInfo& di, int D) {
 
 extern "C" size_t hkv_decode_workspace_bytes(int B, int KVH, int G, int D, int qlmax) {
   using namespace hkv;
-  if (B < 1 || B > kMaxBatch || KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > RPAD || (D != 128 && D != 256)) return 0;
+  if (B < 1 || B > kMaxBatch || KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > kMaxRows || (D != 128 && D != 256)) return 0;
   DeviceInfo* di;
   if (device_info(&di) != HKV_OK) return 0;
   return WorkspaceLayout(max_parts(*di, D), RPAD, D).total;
@@ -840,7 +843,7 @@ extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const 
       !workspace || !out)
     return HKV_ERR_NULL;
   if (D != 128 && D != 256) return HKV_ERR_UNSUPPORTED;
-  if (KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > RPAD) return HKV_ERR_UNSUPPORTED;
+  if (KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > kMaxRows) return HKV_ERR_UNSUPPORTED;
   if (PS < 16 || (PS & (PS - 1)) != 0) return HKV_ERR_UNSUPPORTED;   // 16, 32, 64, ..
   if (B > kMaxBatch) return HKV_ERR_RANGE;
   if (splits < 0) return HKV_ERR_RANGE;
@@ -889,7 +892,22 @@ extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const 
                                            : (layout == 0 ? decode_kernel<256, 0> : decode_kernel<256, 1>);
   const size_t smem_bytes = D == 128 ? (size_t)Smem<128, 0>::TOTAL : (size_t)Smem<256, 0>::TOTAL;
   static_assert(Smem<128, 0>::TOTAL == Smem<128, 1>::TOTAL && Smem<256, 0>::TOTAL == Smem<256, 1>::TOTAL, "layouts share a size");
-  return record_cuda(launch_pdl(k, dim3(grid), dim3(NTHREADS), smem_bytes, st, p));
+  // More than RPAD query rows per kv head (large groups, several draft tokens) are served RPAD rows at a time: every
+  // pass is a decode launch over the cache plus its combine; the last pass's combine is left to hkv_combine.
+  void (*kc)(const uint8_t*, const int*, __nv_bfloat16*, int, int, int, int, float) =
+      D == 128 ? combine_kernel<128> : combine_kernel<256>;
+  const unsigned cgrid = (unsigned)max_parts(*di, D);
+  for (int row0 = 0; row0 < G * qlmax; row0 += RPAD) {
+    p.row0 = row0;
+    rc = record_cuda(launch_pdl(k, dim3(grid), dim3(NTHREADS), smem_bytes, st, p));
+    if (rc != HKV_OK) return rc;
+    if (row0 + RPAD < G * qlmax) {
+      rc = record_cuda(launch_pdl(kc, dim3(cgrid), dim3(128), 0, st, (const uint8_t*)workspace,
+                                  (const int*)query_start_loc, (__nv_bfloat16*)out, KVH, G, qlmax, row0, v_scale));
+      if (rc != HKV_OK) return rc;
+    }
+  }
+  return HKV_OK;
 }
 
 extern "C" int hkv_combine(const void* workspace, size_t workspace_bytes, const int32_t* query_start_loc, int B,
@@ -899,7 +917,7 @@ extern "C" int hkv_combine(const void* workspace, size_t workspace_bytes, const 
   if (B == 0) return HKV_OK;
   if (!workspace || !query_start_loc || !out) return HKV_ERR_NULL;
   if (D != 128 && D != 256) return HKV_ERR_UNSUPPORTED;
-  if (KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > RPAD) return HKV_ERR_UNSUPPORTED;
+  if (KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > kMaxRows) return HKV_ERR_UNSUPPORTED;
   if (((uintptr_t)workspace & 255) || ((uintptr_t)out & 15)) return HKV_ERR_ALIGN;
   if (workspace_bytes < sizeof(Header)) return HKV_ERR_WORKSPACE;
   DeviceInfo* di;
@@ -910,10 +928,11 @@ extern "C" int hkv_combine(const void* workspace, size_t workspace_bytes, const 
   const unsigned grid = (unsigned)max_parts(*di, D);
   if (workspace_bytes < WorkspaceLayout(1, RPAD, D).total) return HKV_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
-  void (*k)(const uint8_t*, const int*, __nv_bfloat16*, int, int, int, float) =
+  void (*k)(const uint8_t*, const int*, __nv_bfloat16*, int, int, int, int, float) =
       D == 128 ? combine_kernel<128> : combine_kernel<256>;
+  const int row0 = (G * qlmax - 1) / RPAD * RPAD;     // the last pass of hkv_decode
   return record_cuda(launch_pdl(k, dim3(grid), dim3(128), 0, st, (const uint8_t*)workspace, (const int*)query_start_loc,
-                                (__nv_bfloat16*)out, KVH, G, qlmax, v_scale));
+                                (__nv_bfloat16*)out, KVH, G, qlmax, row0, v_scale));
 }
 
 extern "C" int hkv_set_option(int option, int value) {
@@ -954,7 +973,7 @@ extern "C" int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf
   if (B < 0 || MP < 0 || splits < 0) return HKV_ERR_RANGE;
   if (B == 0) return HKV_OK;
   if (D != 128 && D != 256) return HKV_ERR_UNSUPPORTED;
-  if (KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > RPAD) return HKV_ERR_UNSUPPORTED;
+  if (KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > kMaxRows) return HKV_ERR_UNSUPPORTED;
   if (splits > 64) return HKV_ERR_SPLITS;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);

@@ -29,7 +29,7 @@ extern "C" {
 #define HKV_OK 0
 #define HKV_ERR_NULL (-1)         /* a required pointer is null */
 #define HKV_ERR_ALIGN (-2)        /* a pointer or stride misses the alignment the kernels need */
-#define HKV_ERR_UNSUPPORTED (-3)  /* head_dim, group size, page size, query length or layout outside the supported set */
+#define HKV_ERR_UNSUPPORTED (-3)  /* head_dim, group size (G * qlmax > 64), page size or layout outside the supported set */
 #define HKV_ERR_SPLITS (-4)       /* more than 64 splits requested */
 #define HKV_ERR_WORKSPACE (-5)    /* workspace too small */
 #define HKV_ERR_RANGE (-6)        /* a size is negative or too large */
@@ -77,6 +77,9 @@ size_t hkv_decode_workspace_bytes(int B, int KVH, int G, int D, int qlmax);
  *   block_tables : int32 (B, MP); seq_lens int32 (B); query_start_loc int32 (B + 1)
  *   requests with 0 or more than qlmax query tokens are skipped and their output rows left untouched
  *   out          : bf16 (>= n_tokens, KVH*G, D) contiguous
+ * A pass over the cache serves 8 query rows per kv head. G * qlmax <= 8 is one decode launch. Up to 64 rows are
+ * accepted: the call then makes ceil(G * qlmax / 8) passes (a decode launch and, for all but the last pass, its
+ * combine launch), still followed by one hkv_combine.
  */
 int hkv_decode(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
                const int64_t strides[6], int PS, const int32_t* block_tables, int MP, const int32_t* seq_lens,

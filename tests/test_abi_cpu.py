@@ -66,8 +66,8 @@ def test_decode_rejects_misuse(lib):
     assert call(q=None) == -1
     assert call(ws=None) == -1
     assert call(D=64) == -3
-    assert call(G=16) == -3                                  # more than 8 query rows per kv head
-    assert call(qlmax=4) == -3
+    assert call(G=65) == -3                                  # more than 64 query rows per kv head
+    assert call(qlmax=17) == -3
     assert call(PS=8) == -3
     assert call(PS=24) == -3
     assert call(splits=65) == -4
@@ -84,7 +84,7 @@ def test_combine_rejects_misuse(lib):
     assert lib.hkv_combine(None, 1 << 20, one, 4, 8, 4, 128, 1, 1.0, one, None) == -1
     assert lib.hkv_combine(one, 1 << 20, one, 4, 8, 4, 96, 1, 1.0, one, None) == -3
     assert lib.hkv_combine(one, 1 << 20, one, 0, 8, 4, 128, 1, 1.0, one, None) == 0
-    assert lib.hkv_combine(one, 1 << 20, one, 4, 8, 9, 128, 1, 1.0, one, None) == -3
+    assert lib.hkv_combine(one, 1 << 20, one, 4, 8, 65, 128, 1, 1.0, one, None) == -3
 
 
 def test_set_option_codes(lib):

@@ -56,10 +56,10 @@ def test_impl_constructor_checks():
         I(32, 128, 0.1, num_kv_heads=8, kv_cache_dtype="nvfp4", sliding_window=128)
     with pytest.raises(ValueError):
         I(32, 128, 0.1, num_kv_heads=8, kv_cache_dtype="nvfp4", sinks=torch.zeros(1))
+    assert I(32, 128, 0.1, num_kv_heads=2, kv_cache_dtype="nvfp4").G == 16     # 16 query rows per kv head: two passes
+    assert I(32, 128, 0.1, num_kv_heads=8, kv_cache_dtype="nvfp4", num_speculative_tokens=3).qlmax == 4
     with pytest.raises(ValueError):
-        I(32, 128, 0.1, num_kv_heads=2, kv_cache_dtype="nvfp4")            # 16 query rows per kv head
-    with pytest.raises(ValueError):
-        I(32, 128, 0.1, num_kv_heads=8, kv_cache_dtype="nvfp4", num_speculative_tokens=3)
+        I(128, 128, 0.1, num_kv_heads=1, kv_cache_dtype="nvfp4")           # 128 query rows per kv head
 
 
 def cam(qsl, seq_lens, MP=4):

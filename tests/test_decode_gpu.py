@@ -200,10 +200,28 @@ def test_graph_replay_with_poisoned_output():
     assert_close(out, oracle_decode(c2))
 
 
+@pytest.mark.parametrize("KVH,G,D,qls", [(2, 16, 128, [1, 1, 1]), (8, 4, 128, [4, 2, 4]), (2, 8, 256, [3, 1, 2]),
+                                         (1, 12, 128, [5, 5, 1])])
+def test_more_than_eight_query_rows(KVH, G, D, qls):
+    """G * ql > 8 rows per kv head (large groups, several draft tokens): served eight rows per pass over the cache;
+    causal among the request's own query tokens; requests with fewer query tokens drop out of the later passes"""
+    lens = [333, 40, 1500][:len(qls)]
+    c = build_decode_case(2450 + G, lens, KVH, G, D, 16, ql_list=qls)
+    ref = oracle_decode(c)
+    NT = c["q"].shape[0]
+    out = torch.full((NT + 2, KVH * G, D), 5.0, dtype=torch.bfloat16, device="cuda")
+    out, ws = gpu_decode(c, out=out, qlmax=max(qls))
+    assert K.workspace_status(ws) == 0
+    assert_close(out, ref, f"G{G} ql{qls}")
+    assert (out[NT:] == 5.0).all()
+    out2 = torch.full_like(out, 5.0)
+    gpu_decode(c, out=out2, ws=ws, qlmax=max(qls), splits=2)
+    assert_close(out2, ref, "splits 2")
+
+
 def test_unsupported_shapes_raise():
-    c = build_decode_case(2400, [40], 2, 16, 128, 16, writer="oracle")     # 16 query rows per kv head
     with pytest.raises(_lib.HkvError):
-        K.alloc_workspace(1, 2, 16, 128, 1)
+        K.alloc_workspace(1, 1, 65, 128, 1)                                # more than 64 query rows per kv head
     c = build_decode_case(2401, [40], 2, 4, 128, 16, kind="nhd", writer="oracle")
     with pytest.raises(_lib.HkvError, match="unsupported"):
         gpu_decode(c)

@@ -50,5 +50,5 @@ def test_noalloc_rejects_what_does_not_fit_or_is_unsupported():
     L = _lib.load()
     assert call_noalloc(c, out, splits=65) == -4
     assert b"scratch" in L.hkv_error_string(-9)
-    c2 = dict(c, G=16)
+    c2 = dict(c, G=65)                                            # more than 64 query rows per kv head
     assert call_noalloc(c2, out) == -3
