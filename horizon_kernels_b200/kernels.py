@@ -123,6 +123,53 @@ def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_
     return out
 
 
+def _dequant(flat, strides, PS, block_tables, MP, rows, cu, n_rows, start, n_tokens, out_k, out_v, k8):
+    if k8:
+        raise NotImplementedError("the K8V4 slot is not built")
+    _need_cuda(block_tables, out_k, out_v, *flat)
+    if out_k.dtype not in (torch.bfloat16, torch.float16) or out_v.dtype != out_k.dtype:
+        raise TypeError("out_k / out_v must both be bf16 or both fp16")
+    if not out_k.is_contiguous() or not out_v.is_contiguous() or out_k.shape != out_v.shape:
+        raise ValueError("out_k / out_v must be contiguous (n, KVH, D) tensors of one shape")
+    if out_k.shape[0] < n_tokens:
+        raise ValueError("output buffers shorter than the number of tokens")
+    if block_tables.dtype != torch.int32 or not block_tables.is_contiguous():
+        raise TypeError("block tables must be contiguous int32")
+    KVH, D = out_k.shape[1], out_k.shape[2]
+    kd, ksf, vd, vsf = flat
+    st = (C.c_int64 * 6)(*strides)
+    with torch.cuda.device(out_k.device):
+        rc = _lib.load().hkv_dequant(_ptr(kd), _ptr(ksf), _ptr(vd), _ptr(vsf), st, int(PS), _ptr(block_tables), int(MP),
+                                     None if rows is None else _ptr(rows), None if cu is None else _ptr(cu), int(n_rows),
+                                     int(start), int(n_tokens), _ptr(out_k), _ptr(out_v), KVH, D,
+                                     int(out_k.dtype == torch.float16), _stream())
+    _lib.check(rc, "hkv_dequant")
+
+
+def dequant_tokens(flat, strides, PS, block_table_row, start, n, out_k, out_v, k8=False):
+    """positions [start, start + n) of one request (its block-table row, int32) -> out_k / out_v[:n], (n, KVH, D) bf16
+    or fp16 by the output dtype: e2m1 * e4m3, exact, no global scale. Signature of kv_fp4_serving.py:918."""
+    if block_table_row.dim() != 1:
+        raise ValueError("block_table_row is the 1-D block-table row of one request")
+    if (start + n + PS - 1) // PS > block_table_row.shape[0]:
+        raise ValueError("positions beyond the block-table row")
+    _dequant(flat, strides, PS, block_table_row, block_table_row.shape[0], None, None, 0, start, n, out_k, out_v, k8)
+    return out_k[:n], out_v[:n]
+
+
+def dequant_multi(flat, strides, PS, block_tables, rows, cu, n_rows, n_tokens, out_k, out_v, k8=False):
+    """full contexts of requests rows[r] (int32, device), packed: out_k / out_v[cu[r]:cu[r + 1]] = request rows[r];
+    cu (n_rows + 1,) int32 device with cu[n_rows] == n_tokens. Exact, no global scale.
+    Signature of kv_fp4_serving.py:1008."""
+    _need_cuda(rows, cu)
+    for t in (rows, cu):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise TypeError("rows / cu must be contiguous int32")
+    if block_tables.dim() != 2 or cu.shape[0] < n_rows + 1 or rows.shape[0] < n_rows:
+        raise ValueError("block_tables (B, MP); rows (>= n_rows,); cu (>= n_rows + 1,)")
+    _dequant(flat, strides, PS, block_tables, block_tables.shape[1], rows, cu, n_rows, 0, n_tokens, out_k, out_v, k8)
+
+
 OPT_EARLY_METADATA = 1
 
 

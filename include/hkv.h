@@ -124,6 +124,25 @@ int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf, const voi
                        float v_scale, const float* gk, const float* gv, int splits, void* out, void* stream);
 
 /*
+ * Exact dequantisation of cached tokens into dense bf16 or fp16 rows (n_tokens, KVH, D), the input of a prefill
+ * attention over a cached prefix: value = e2m1(code) * e4m3(block scale), WITHOUT the global scales gk / gv (the
+ * product is exact in both output types; the caller folds the global scales into its softmax scale and its output).
+ * Replaces `dequant_tokens` / `hz4::dequant_task` (kv_fp4_serving.py:918-925, :577-609) and `dequant_multi` /
+ * `hz4::dequant_multi_task` (kv_fp4_serving.py:1008-1016, :700-740).
+ *   rows == NULL, cu == NULL : one request. `block_tables` points at ITS block-table row; positions
+ *                              [start, start + n_tokens) of its context go to output rows [0, n_tokens).
+ *   rows, cu given           : requests rows[r], r < n_rows, with their full contexts packed: output rows
+ *                              [cu[r], cu[r + 1]) hold positions 0 .. cu[r + 1] - cu[r] - 1 of request rows[r];
+ *                              cu[0] == 0, cu[n_rows] == n_tokens; `block_tables` is the (B, MP) table; `start` unused.
+ *   out_k, out_v             : (n_tokens, KVH, D) contiguous, bf16 (out_f16 == 0) or fp16 (out_f16 == 1), 16-byte aligned
+ * Any of the cache layouts hkv_write accepts (code rows 8-byte aligned). A scale byte 0x7f / 0xff (never written by
+ * hkv_write) gives NaN.
+ */
+int hkv_dequant(const void* kd, const void* ksf, const void* vd, const void* vsf, const int64_t strides[6], int PS,
+                const int32_t* block_tables, int MP, const int32_t* rows, const int32_t* cu, int n_rows, int64_t start,
+                int64_t n_tokens, void* out_k, void* out_v, int KVH, int D, int out_f16, void* stream);
+
+/*
  * Process-wide options. No counterpart in the reference.
  *   HKV_OPT_EARLY_METADATA (0 = off, the default; 1 = on): the caller states that `seq_lens` and `query_start_loc` of
  *     every later hkv_decode / hkv_decode_noalloc call are complete before the kernel that PRECEDES the call on its

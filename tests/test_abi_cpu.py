@@ -87,6 +87,24 @@ def test_combine_rejects_misuse(lib):
     assert lib.hkv_combine(one, 1 << 20, one, 4, 8, 65, 128, 1, 1.0, one, None) == -3
 
 
+def test_dequant_rejects_misuse(lib):
+    one = C.c_void_p(0x1000)
+    st = (C.c_int64 * 6)(1152 * 16, 72, 1152, 1152 * 16, 72, 1152)
+    f = lib.hkv_dequant
+
+    def call(kd=one, rows=None, cu=None, n_rows=0, start=0, n=4, D=128, KVH=8, ok=one):
+        return f(kd, one, one, one, st, 16, one, 4, rows, cu, n_rows, start, n, ok, one, KVH, D, 0, None)
+    assert call(kd=None) == -1
+    assert call(rows=one) == -1                                # rows without cu
+    assert call(rows=one, cu=one, n_rows=0) == -6
+    assert call(D=64) == -3
+    assert call(KVH=0) == -3
+    assert call(n=-1) == -6
+    assert call(start=-1) == -6
+    assert call(n=0) == 0
+    assert call(ok=C.c_void_p(0x1008)) == -2
+
+
 def test_set_option_codes(lib):
     assert lib.hkv_set_option(99, 1) == -3
     assert lib.hkv_set_option(1, 2) == -6
