@@ -10,8 +10,10 @@
 
 The classes derive from vLLM's base classes when vLLM has already been imported by the process (that is, when vLLM
 loads this plugin); otherwise from small stand-ins, so the surface can be exercised and benchmarked without importing
-vLLM. Only the decode path is built: a step that contains prefill rows (more query tokens than the decode threshold)
-raises NotImplementedError instead of silently producing nothing. There is no fallback to another backend.
+vLLM. Rows with more query tokens than the decode threshold (prefill over a cached prefix) take the exact
+dequantisation kernel followed by torch's scaled_dot_product_attention per request (a library attention, as the
+reference uses FlashInfer's FA2 there, backend.py:517-543); that path is eager and outside the timed hot path. There is
+no fallback to another backend.
 """
 import os
 import sys
@@ -286,9 +288,6 @@ def _build_classes():
             if output_scale is not None or output_block_scale is not None:
                 raise ValueError("fused output quantisation is not supported")
             m = attn_metadata
-            if m.prefill_rows:
-                raise NotImplementedError("horizon_kvfp4 (B200): the prefill path is not built; this step has "
-                                          f"{len(m.prefill_rows)} request(s) with more than {m.decode_threshold} query tokens")
             T = m.num_actual_tokens
             st = self._state(query.device)
             v = self._cache_views(kv_cache)
@@ -303,7 +302,33 @@ def _build_classes():
                 K.decode_ragged(q, v["flat"], v["strides"], v["PS"], m.block_table, m.seq_lens, m.query_start_loc,
                                 self.scale, float(layer._v_scale_float), gk, gv, m.qlmax, out, st["ws"],
                                 splits=self.cps or None)
+            if m.prefill_rows:
+                self._prefill_rows(layer, q, v, m, out)
             return output
+
+        def _prefill_rows(self, layer, q, v, m, out):
+            """requests with more query tokens than the decode threshold: exact dequantisation of the request's context
+            (the new tokens were written by do_kv_cache_update) to bf16, then attention over it with the causal window
+            of the reference (query token t of ql sees keys j < L - ql + t + 1). The global scales are folded into the
+            softmax scale and the output like the reference's sm / vs (backend.py:517-543). Eager, one request at a
+            time; the mask costs ql * L bytes."""
+            sm = self.scale * float(layer._k_scale_float)
+            vs = float(layer._v_scale_float)
+            KVH, D = self.num_kv_heads, self.head_size
+            for row, q0, q1, L in m.prefill_rows:
+                ql = q1 - q0
+                if ql <= 0 or L <= 0:
+                    continue
+                kk = torch.empty((L, KVH, D), dtype=torch.bfloat16, device=q.device)
+                vv = torch.empty_like(kk)
+                K.dequant_tokens(v["flat"], v["strides"], v["PS"], m.block_table[row].contiguous(), 0, L, kk, vv)
+                qi = q[q0:q1].transpose(0, 1).unsqueeze(0)                       # (1, HQ, ql, D)
+                mask = torch.ones((ql, L), dtype=torch.bool, device=q.device).tril_(diagonal=L - ql)
+                o = torch.nn.functional.scaled_dot_product_attention(
+                    qi, kk.transpose(0, 1).unsqueeze(0), vv.transpose(0, 1).unsqueeze(0), attn_mask=mask, scale=sm,
+                    enable_gqa=True)
+                o = o.squeeze(0).transpose(0, 1)                                 # (ql, HQ, D)
+                out[q0:q1].copy_(o * vs if vs != 1.0 else o)
 
     return dict(HorizonFp4Backend=HorizonFp4Backend, HorizonFp4Metadata=HorizonFp4Metadata,
                 HorizonFp4Builder=HorizonFp4Builder, HorizonFp4Impl=HorizonFp4Impl)

@@ -84,13 +84,12 @@ def test_builder_splits_decode_and_prefill_rows():
     assert m.decode_threshold == 2 and m.qlmax == 2 and m.prefill_rows == []
 
 
-def test_forward_refuses_prefill_rows_and_profiling_run_returns_output():
+def test_profiling_run_returns_output_and_output_quantisation_is_refused():
     impl = BE.HorizonFp4Impl(32, 128, 0.088, num_kv_heads=8, kv_cache_dtype="nvfp4")
     out = torch.zeros(4, 32 * 128, dtype=torch.bfloat16)
     assert impl.forward(None, out, None, None, None, None, out) is out
     m = BE.HorizonFp4Builder().build(0, cam([0, 1, 9], [10, 200]))
-    with pytest.raises(NotImplementedError, match="prefill"):
-        impl.forward(SimpleNamespace(_k_scale_float=1.0, _v_scale_float=1.0), out, None, None, None, m, out)
+    assert m.prefill_rows == [(1, 1, 9, 200)] and m.has_decode
     with pytest.raises(ValueError):
         impl.forward(None, out, None, None, None, m, out, output_scale=torch.ones(1))
 

@@ -53,3 +53,52 @@ def test_update_then_forward_matches_oracle(KVH, G, D, PS):
     scale = 1.0 / vscale                            # the output carries the extra v_scale factor: compare at unit scale
     assert_close(output[:B].view(B, HQ, D).float() * scale, ref * scale)
     assert (output[B:] == 5.0).all()
+
+
+@pytest.mark.parametrize("KVH,G,D,PS", [(8, 4, 128, 16), (2, 8, 256, 16)])
+def test_mixed_step_with_prefill_rows(KVH, G, D, PS):
+    """a step with decode rows (1 query token) and prefill rows over a cached prefix (37 and 300 query tokens): the
+    decode kernel serves the former and leaves the latter untouched, the dequantise + attention path serves the latter;
+    both against the oracle with the reference's causal window"""
+    lens = [300, 37, 2049, 64, 700]
+    qls = [1, 37, 1, 1, 300]
+    c = synth.paged_case(77 + D, lens, KVH, G, D, PS, outliers=True, ql_list=qls)
+    dev = torch.device("cuda")
+    B, HQ, NT = len(lens), KVH * G, sum(qls)
+    kscale, vscale = 0.04, 0.5
+    layer = SimpleNamespace(_k_scale_float=kscale, _v_scale_float=vscale, layer_name="model.layers.0.self_attn.attn")
+    impl = BE.HorizonFp4Impl(HQ, D, D ** -0.5, num_kv_heads=KVH, kv_cache_dtype="nvfp4", max_num_seqs=16)
+    kv_cache = Lt.alloc_cache(c["NP"], PS, KVH, D, device=dev, fill=0x7F)
+    impl.do_kv_cache_update(layer, bf16_tensor(c["key"]).view(-1, KVH * D), bf16_tensor(c["val"]).view(-1, KVH * D),
+                            kv_cache, torch.from_numpy(c["slots"]).to(dev))
+    qsl = torch.from_numpy(c["qsl"])
+    cam = SimpleNamespace(num_reqs=B, num_actual_tokens=NT, query_start_loc=qsl.to(dev), query_start_loc_cpu=qsl,
+                          seq_lens=torch.from_numpy(c["seq_lens"]).to(dev),
+                          block_table_tensor=torch.from_numpy(c["bt"]).to(dev),
+                          slot_mapping=torch.zeros(NT, dtype=torch.int64, device=dev),
+                          seq_lens_cpu_upper_bound=torch.from_numpy(c["seq_lens"]))
+    meta = BE.HorizonFp4Builder().build(0, cam)
+    assert [r[0] for r in meta.prefill_rows] == [1, 4] and meta.has_decode and meta.qlmax == 1
+    query = bf16_tensor(c["q"]).view(NT, HQ * D)
+    output = torch.full((NT, HQ * D), 5.0, dtype=torch.bfloat16, device=dev)
+    impl.forward(layer, query, None, None, kv_cache, meta, output)
+    lay = O.Layout.slots(PS, KVH, D)
+    gk = np.full(KVH, kscale, np.float32)
+    gv = np.full(KVH, vscale, np.float32)
+    ref, _ = O.attention(c["q"], kv_cache.cpu().numpy().reshape(-1), lay, c["bt"], c["seq_lens"], c["qsl"], KVH,
+                         D ** -0.5, gk, gv, 1.0)
+    # like the reference, the decode path multiplies by the V scale twice (gv and bmm2_scale are both
+    # layer._v_scale_float, backend.py:431) and the prefill path once (backend.py:523-541): compare at unit scale
+    from cases import errors
+    got = output.view(NT, HQ, D).float() / vscale
+    want = ref / vscale
+    dec = np.zeros(NT, bool)
+    for b in range(B):
+        if qls[b] == 1:
+            dec[int(c["qsl"][b])] = True
+    got[torch.from_numpy(dec).to(dev)] /= vscale
+    assert_close(got[torch.from_numpy(dec).to(dev)], want[dec], "decode rows")
+    # prefill rows go through a library bf16 attention (probabilities rounded to bf16): the reference's own gate,
+    # relative L2, holds; the absolute error scales with the outputs, which reach the values' outliers here
+    mx, mn, rl = errors(got[torch.from_numpy(~dec).to(dev)], want[~dec])
+    assert rl <= 2.5e-3 and mn <= 2e-3 and mx <= 6e-2, (mx, mn, rl)
