@@ -147,8 +147,37 @@ def dequantize_rows(data, sf, g=None):
     return out.reshape(*data.shape[:-1], D)
 
 
-def write(key, value, cache, layout: Layout, slots, gk, gv, search=True):
-    """key / value (NT, KVH, D) uint16 (bf16 bits), C-contiguous; cache flat uint8 (modified in place); slots int64"""
+def fwht_scale(D: int) -> np.float32:
+    """D^-0.5 rounded to fp32 (kv_fp4_ref.py:52-54)"""
+    return np.float32(1.0 / np.sqrt(np.float64(D)))
+
+
+def rotate(x, signs):
+    """x (..., D) float32 -> fp32 FWHT(x * signs) * D^-0.5 in the reference's butterfly order (kv_fp4_ref.py:83-87)"""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    D = x.shape[-1]
+    assert D <= 512 and D & (D - 1) == 0
+    signs = np.ascontiguousarray(signs, dtype=np.float32)
+    out = np.empty_like(x)
+    lib().hkvo_rotate_rows(_p(x), C.c_longlong(x.size // D), C.c_int(D), _p(signs), C.c_float(fwht_scale(D)), _p(out))
+    return out
+
+
+def f32_to_bf16_bits(x):
+    """round to nearest even, like torch's .to(bfloat16) for finite values"""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def rotate_q(q_bits, signs):
+    """bf16 bits of the query the decode consumes when keys are rotated: rotate() rounded once to bf16
+    (kv_fp4_ref.py:90-92)"""
+    return f32_to_bf16_bits(rotate(bf16_to_f32(q_bits), signs))
+
+
+def write(key, value, cache, layout: Layout, slots, gk, gv, search=True, signs=None):
+    """key / value (NT, KVH, D) uint16 (bf16 bits), C-contiguous; cache flat uint8 (modified in place); slots int64;
+    signs (D,) fp32 -> the keys are rotated before they are quantised"""
     key = np.ascontiguousarray(key, dtype=np.uint16)
     value = np.ascontiguousarray(value, dtype=np.uint16)
     NT, KVH, D = key.shape
@@ -157,9 +186,11 @@ def write(key, value, cache, layout: Layout, slots, gk, gv, search=True):
     gk = np.ascontiguousarray(gk, dtype=np.float32)
     gv = np.ascontiguousarray(gv, dtype=np.float32)
     lay = layout.c()
-    lib().hkvo_write(_p(key), _p(value), C.c_longlong(KVH * D), C.c_longlong(D), C.c_longlong(KVH * D),
-                     C.c_longlong(D), _p(cache), C.byref(lay), _p(slots), C.c_longlong(slots.shape[0]), _p(gk),
-                     _p(gv), C.c_int(KVH), C.c_int(D), C.c_int(int(bool(search))))
+    sg = None if signs is None else np.ascontiguousarray(signs, dtype=np.float32)
+    lib().hkvo_write_rot(_p(key), _p(value), C.c_longlong(KVH * D), C.c_longlong(D), C.c_longlong(KVH * D),
+                         C.c_longlong(D), _p(cache), C.byref(lay), _p(slots), C.c_longlong(slots.shape[0]), _p(gk),
+                         _p(gv), C.c_int(KVH), C.c_int(D), C.c_int(int(bool(search))),
+                         None if sg is None else _p(sg), C.c_float(fwht_scale(D)))
 
 
 def attention(q, cache, layout: Layout, block_tables, seq_lens, query_start_loc, KVH, sm_scale, gk, gv, v_scale=1.0,

@@ -161,6 +161,26 @@ void hkvo_dequantize_rows(const uint8_t* data, const uint8_t* sf, long long n_ro
     }
 }
 
+/* rotate (kv_fp4_ref.py:55-87): out = FWHT(x * signs) * D^-0.5 in fp32, butterflies in the reference's stage order
+ * (h = 1, 2, 4, .., D/2; for every i with (i & h) == 0: (x[i], x[i+h]) = (x[i] + x[i+h], x[i] - x[i+h])).
+ * `scale` is D^-0.5 rounded to fp32 by the caller. x and out may be the same array. */
+void hkvo_rotate_row(const float* x, const float* signs, int D, float scale, float* out) {
+  for (int i = 0; i < D; ++i) { volatile float v = x[i] * signs[i]; out[i] = v; }
+  for (int h = 1; h < D; h *= 2)
+    for (int i = 0; i < D; ++i)
+      if ((i & h) == 0) {
+        volatile float a = out[i], b = out[i + h];
+        volatile float s = a + b, d = a - b;
+        out[i] = s;
+        out[i + h] = d;
+      }
+  for (int i = 0; i < D; ++i) { volatile float v = out[i] * scale; out[i] = v; }
+}
+void hkvo_rotate_rows(const float* x, long long n_rows, int D, const float* signs, float scale, float* out) {
+#pragma omp parallel for schedule(static)
+  for (long long r = 0; r < n_rows; ++r) hkvo_rotate_row(x + r * D, signs, D, scale, out + r * D);
+}
+
 /* The four cache parts as [page, position, head, byte] views of one byte buffer (kv_fp4_ref.py:215-230 and
  * backend.py:279-300): byte offsets of the parts plus data strides (page, position, head) and scale strides. */
 typedef struct {
@@ -170,30 +190,35 @@ typedef struct {
   int PS;
 } hkvo_layout;
 
-/* write_reference (kv_fp4_ref.py:233-245) without the optional rotation: key/value (NT, KVH, D) bf16 with element
- * strides (token, head), slot < 0 skipped, one global scale per kv head and side. */
-void hkvo_write(const uint16_t* key, const uint16_t* val, long long ks0, long long ks1, long long vs0, long long vs1,
-                uint8_t* cache, const hkvo_layout* lay, const long long* slots, long long n_slots, const float* gk,
-                const float* gv, int KVH, int D, int search) {
+/* write_reference (kv_fp4_ref.py:233-245): key/value (NT, KVH, D) bf16 with element strides (token, head), slot < 0
+ * skipped, one global scale per kv head and side. signs != NULL: the keys are rotated first (hkvo_rotate_row) and
+ * quantised from the fp32 result; values are never rotated. */
+void hkvo_write_rot(const uint16_t* key, const uint16_t* val, long long ks0, long long ks1, long long vs0,
+                    long long vs1, uint8_t* cache, const hkvo_layout* lay, const long long* slots, long long n_slots,
+                    const float* gk, const float* gv, int KVH, int D, int search, const float* signs, float rot_scale) {
   const int nb = D / HKVO_BLOCK;
 #pragma omp parallel for schedule(static)
   for (long long t = 0; t < n_slots; ++t) {
     long long sl = slots[t];
     if (sl < 0) continue;
     long long p = sl / lay->PS, o = sl % lay->PS;
-    float x[HKVO_BLOCK];
+    float row[512];
     for (int side = 0; side < 2; ++side)
       for (int h = 0; h < KVH; ++h) {
         const uint16_t* src = side ? val + t * vs0 + h * vs1 : key + t * ks0 + h * ks1;
         uint8_t* dd = cache + (side ? lay->vd : lay->kd) + p * lay->dsp + o * lay->dst + h * lay->dsh;
         uint8_t* ds = cache + (side ? lay->vsf : lay->ksf) + p * lay->ssp + o * lay->sst + h * lay->ssh;
         float g = side ? gv[h] : gk[h];
-        for (int b = 0; b < nb; ++b) {
-          for (int i = 0; i < HKVO_BLOCK; ++i) x[i] = bf16_f32(src[b * 16 + i]);
-          hkvo_quantize_block(x, g, search, dd + b * 8, ds + b);
-        }
+        for (int i = 0; i < D; ++i) row[i] = bf16_f32(src[i]);
+        if (signs && side == 0) hkvo_rotate_row(row, signs, D, rot_scale, row);
+        for (int b = 0; b < nb; ++b) hkvo_quantize_block(row + b * 16, g, search, dd + b * 8, ds + b);
       }
   }
+}
+void hkvo_write(const uint16_t* key, const uint16_t* val, long long ks0, long long ks1, long long vs0, long long vs1,
+                uint8_t* cache, const hkvo_layout* lay, const long long* slots, long long n_slots, const float* gk,
+                const float* gv, int KVH, int D, int search) {
+  hkvo_write_rot(key, val, ks0, ks1, vs0, vs1, cache, lay, slots, n_slots, gk, gv, KVH, D, search, 0, 0.0f);
 }
 
 /* attention_reference (kv_fp4_ref.py:260-280) with per-request query lengths (kv_fp4_serving.py:5-11): fp64 attention

@@ -166,6 +166,40 @@ def config0(R):
     return dict(bt=bt, gk=gk, gv=gv, ref=ref.numpy(), cache_sha256=np.array(sha), sm=np.array([sm]))
 
 
+def rotation_cases(R):
+    """the optional key rotation: the reference's sign vectors, rotate() of bf16 rows in fp32, rotate_q() (one rounding
+    to bf16), and caches written with rotated keys (region layout, search on and off)"""
+    out = {}
+    for D in (128, 256):
+        signs = R.hadamard_signs(D)
+        x = synth.normal(700 + D, (24, D)) * np.exp(synth.normal(710 + D, (24, 1)))
+        x[0] = 0.0
+        x[1, 5] = 1e4
+        xb = synth.to_bf16_bits(x)
+        out[f"signs{D}"] = signs.numpy()
+        out[f"x{D}"] = xb
+        out[f"rot{D}"] = R.rotate(bf16(xb), signs).numpy()
+        out[f"rotq{D}"] = R.rotate_q(bf16(xb), signs).view(torch.int16).numpy().view(np.uint16)
+        out[f"scale{D}"] = np.array([R.fwht_scale(D)], np.float32)
+        KVH, PS, NT = 2, 16, 50
+        NP = (NT + PS - 1) // PS + 2
+        k = synth.normal(720 + D, (NT, KVH, D)) * 2.0
+        k[:, :, [3, D // 2 + 3]] *= 20.0
+        v = synth.normal(730 + D, (NT, KVH, D))
+        kb, vb = synth.to_bf16_bits(k), synth.to_bf16_bits(v)
+        slots = synth.permutation(740 + D, NP * PS)[:NT].astype(np.int64)
+        gk = np.array([0.05, 0.02], np.float32)
+        gv = np.array([0.01, 0.03], np.float32)
+        out.update({f"w{D}_key": kb, f"w{D}_val": vb, f"w{D}_slots": slots, f"w{D}_gk": gk, f"w{D}_gv": gv,
+                    f"w{D}_geom": np.array([KVH, D, PS, NP], np.int64)})
+        for search in (0, 1):
+            c = R.alloc_cache(NP, PS, KVH, D, fill=0xA5)
+            R.write_reference(bf16(kb), bf16(vb), R.split_views(c, KVH), torch.from_numpy(slots),
+                              torch.from_numpy(gk), torch.from_numpy(gv), signs, bool(search))
+            out[f"w{D}_region_s{search}"] = c.numpy().reshape(-1)
+    return out
+
+
 def main():
     root = sys.argv[1]
     R = load_ref(root)
@@ -174,7 +208,8 @@ def main():
     np.savez_compressed(os.path.join(HERE, "write.npz"), **write_cases(R))
     np.savez_compressed(os.path.join(HERE, "attention.npz"), **attention_cases(R))
     np.savez_compressed(os.path.join(HERE, "config0.npz"), **config0(R))
-    for f in ("quant.npz", "write.npz", "attention.npz", "config0.npz"):
+    np.savez_compressed(os.path.join(HERE, "rotation.npz"), **rotation_cases(R))
+    for f in ("quant.npz", "write.npz", "attention.npz", "config0.npz", "rotation.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
 
