@@ -7,7 +7,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libhkv.so")
 
 EXPORTS = ("hkv_version", "hkv_error_string", "hkv_last_cuda_error", "hkv_write", "hkv_decode_workspace_bytes",
-           "hkv_decode", "hkv_combine", "hkv_workspace_status", "hkv_decode_noalloc", "hkv_set_option", "hkv_dequant")
+           "hkv_decode", "hkv_combine", "hkv_workspace_status", "hkv_decode_noalloc", "hkv_set_option", "hkv_dequant", "hkv_write_rot",
+           "hkv_decode_rot")
 
 _lib = None
 
@@ -47,6 +48,10 @@ def load():
         L.hkv_decode_noalloc.restype = i32
         L.hkv_decode_noalloc.argtypes = [vp, vp, vp, vp, vp, C.POINTER(i64), i32, vp, i32, vp, vp, i32, i32, i32, i32, i32,
                                          f32, f32, vp, vp, i32, vp, vp]
+        L.hkv_write_rot.restype = i32
+        L.hkv_write_rot.argtypes = L.hkv_write.argtypes[:-1] + [vp, vp]
+        L.hkv_decode_rot.restype = i32
+        L.hkv_decode_rot.argtypes = L.hkv_decode.argtypes[:-2] + [vp, vp, vp]
         L.hkv_dequant.restype = i32
         L.hkv_dequant.argtypes = [vp, vp, vp, vp, C.POINTER(i64), i32, vp, i32, vp, vp, i32, i64, i64, vp, vp, i32, i32,
                                   i32, vp]

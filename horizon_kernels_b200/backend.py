@@ -208,8 +208,12 @@ def _build_classes():
             self.kv_sharing_target_layer_name = None
             self.sliding_window = None
             self.G = self.num_heads // self.num_kv_heads
-            if _env("HORIZON_KVFP4_HAD", "0") == "1" or _env("HORIZON_KVFP4_K8", "0") == "1":
-                raise NotImplementedError("key rotation (HORIZON_KVFP4_HAD) and the K8V4 slot (HORIZON_KVFP4_K8) are not built")
+            if _env("HORIZON_KVFP4_K8", "0") == "1":
+                raise NotImplementedError("the K8V4 slot (HORIZON_KVFP4_K8) is not built")
+            # HORIZON_KVFP4_HAD=1: keys are written rotated (Hadamard) and queries rotated inside the decode kernel
+            # (reference backend.py:214-222, kv_fp4_ref.py:31-35)
+            self.had = _env("HORIZON_KVFP4_HAD", "0") == "1"
+            self._signs = None
             self.search = _env("HORIZON_KVFP4_SEARCH", "1") == "1"
             self.cps = int(_env("HORIZON_KVFP4_CPS", "0"))        # splits per (request, kv head); 0 = fill the GPU
             self._gk = self._gv = None
@@ -264,6 +268,14 @@ def _build_classes():
                 self._gv = torch.full((self.num_kv_heads,), float(layer._v_scale_float), device=device)
             return self._gk, self._gv
 
+        def _rot(self, device):
+            """the rotation's sign vector on the device (None without HORIZON_KVFP4_HAD)"""
+            if not self.had:
+                return None
+            if self._signs is None or self._signs.device != device:
+                self._signs = K.hadamard_signs(self.head_size, device=device)
+            return self._signs
+
         def process_weights_after_loading(self, act_dtype):
             """the kernels are compiled ahead of time; only the workspace is made here, outside any CUDA graph"""
             if torch.cuda.is_available():
@@ -277,7 +289,8 @@ def _build_classes():
             D = self.head_size
             k3 = key.view(key.shape[0], self.num_kv_heads, D) if key.dim() == 2 else key
             v3 = value.view(value.shape[0], self.num_kv_heads, D) if value.dim() == 2 else value
-            K.write(k3, v3, v["flat"], v["strides"], v["PS"], slot_mapping, gk, gv, self.search)
+            K.write(k3, v3, v["flat"], v["strides"], v["PS"], slot_mapping, gk, gv, self.search,
+                    signs=self._rot(key.device))
 
         # -------------------------------------------------------------------------------------------- forward
         def forward(self, layer, query, key, value, kv_cache, attn_metadata, output, output_scale=None,
@@ -301,7 +314,7 @@ def _build_classes():
             if m.has_decode and m.num_reqs > 0:
                 K.decode_ragged(q, v["flat"], v["strides"], v["PS"], m.block_table, m.seq_lens, m.query_start_loc,
                                 self.scale, float(layer._v_scale_float), gk, gv, m.qlmax, out, st["ws"],
-                                splits=self.cps or None)
+                                splits=self.cps or None, signs=self._rot(q.device))
             if m.prefill_rows:
                 self._prefill_rows(layer, q, v, m, out)
             return output
@@ -322,7 +335,10 @@ def _build_classes():
                 kk = torch.empty((L, KVH, D), dtype=torch.bfloat16, device=q.device)
                 vv = torch.empty_like(kk)
                 K.dequant_tokens(v["flat"], v["strides"], v["PS"], m.block_table[row].contiguous(), 0, L, kk, vv)
-                qi = q[q0:q1].transpose(0, 1).unsqueeze(0)                       # (1, HQ, ql, D)
+                qi = q[q0:q1]
+                if self.had:                                                     # the cached keys are rotated
+                    qi = K.rotate(qi, self._rot(q.device)).to(torch.bfloat16)
+                qi = qi.transpose(0, 1).unsqueeze(0)                             # (1, HQ, ql, D)
                 mask = torch.ones((ql, L), dtype=torch.bool, device=q.device).tril_(diagonal=L - ql)
                 o = torch.nn.functional.scaled_dot_product_attention(
                     qi, kk.transpose(0, 1).unsqueeze(0), vv.transpose(0, 1).unsqueeze(0), attn_mask=mask, scale=sm,

@@ -25,6 +25,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cmath>
 
 #include "hkv_common.cuh"
 
@@ -56,6 +57,8 @@ struct DecodeParams {
   uint8_t* ws;
   __nv_bfloat16* out;
   int MP, B, KVH, G, qlmax, PS;
+  const float* signs;                                // +-1 per channel when the keys were written rotated, else null
+  float rot_scale;                                   // head_dim^-0.5 rounded to fp32
   int row0;                                          // first query row (of the G * ql rows of a request and kv head) of this pass
   int early_meta;                                    // seq_lens / query_start_loc are read before the launch dependency
   float scale_log2, v_scale;
@@ -424,6 +427,8 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
         const bool have = g < R;
         const int t = have ? (p.row0 + g) / G : 0, gq = have ? p.row0 + g - t * G : 0;
         const __nv_bfloat16* qrow = p.q + ((long long)(q0 + t) * (KVH * G) + h * G + gq) * D;
+        constexpr int NQ = 16 * Gm::NBL;            // this lane's channels: NQ * c .. NQ * c + NQ - 1 of the row
+        float qf[NQ];
 #pragma unroll
         for (int u = 0; u < Gm::NBL; ++u) {
           uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
@@ -435,12 +440,48 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
           const uint32_t ws[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            float a = __uint_as_float(ws[i] << 16), bq = __uint_as_float(ws[i] & 0xffff0000u);
-            a = fminf(fmaxf(a, -65504.0f), 65504.0f);
-            bq = fminf(fmaxf(bq, -65504.0f), 65504.0f);
-            if (flip) { a = -a; bq = -bq; }
-            qa[4 * u + (i >> 1)][i & 1] = pack_f16x2(a, bq);
+            qf[16 * u + 2 * i] = __uint_as_float(ws[i] << 16);
+            qf[16 * u + 2 * i + 1] = __uint_as_float(ws[i] & 0xffff0000u);
           }
+        }
+        if (p.signs != nullptr) {
+          // keys were written rotated: q' = bf16(FWHT(q * signs) * head_dim^-0.5), the reference's rotate_q
+          // (kv_fp4_ref.py:90-92), fp32 butterflies in its stage order. The four lanes of a quad hold one row.
+          const float4* sg = reinterpret_cast<const float4*>(p.signs + NQ * c);
+#pragma unroll
+          for (int i = 0; i < NQ / 4; ++i) {
+            const float4 s4 = __ldg(sg + i);
+            qf[4 * i] = __fmul_rn(qf[4 * i], s4.x);
+            qf[4 * i + 1] = __fmul_rn(qf[4 * i + 1], s4.y);
+            qf[4 * i + 2] = __fmul_rn(qf[4 * i + 2], s4.z);
+            qf[4 * i + 3] = __fmul_rn(qf[4 * i + 3], s4.w);
+          }
+#pragma unroll
+          for (int hh = 1; hh < NQ; hh *= 2)
+#pragma unroll
+            for (int i = 0; i < NQ; ++i)
+              if ((i & hh) == 0) {
+                const float a = qf[i], b = qf[i + hh];
+                qf[i] = __fadd_rn(a, b);
+                qf[i + hh] = __fsub_rn(a, b);
+              }
+#pragma unroll
+          for (int m = 1; m < 4; m *= 2) {          // stages h = NQ, 2 NQ: the partner is the lane with c ^ m
+            const bool upper = (c & m) != 0;
+#pragma unroll
+            for (int i = 0; i < NQ; ++i) {
+              const float o2 = __shfl_xor_sync(0xffffffffu, qf[i], m);
+              qf[i] = upper ? __fsub_rn(o2, qf[i]) : __fadd_rn(qf[i], o2);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < NQ; ++i) qf[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(qf[i], p.rot_scale)));
+        }
+#pragma unroll
+        for (int i = 0; i < NQ / 2; ++i) {
+          float a = fminf(fmaxf(qf[2 * i], -65504.0f), 65504.0f), bq = fminf(fmaxf(qf[2 * i + 1], -65504.0f), 65504.0f);
+          if (flip) { a = -a; bq = -bq; }
+          qa[i >> 1][i & 1] = pack_f16x2(a, bq);
         }
       }
       // visible context of query rows 2c, 2c+1 (causal among the request's own query tokens)
@@ -831,11 +872,11 @@ extern "C" size_t hkv_decode_workspace_bytes(int B, int KVH, int G, int D, int q
   return WorkspaceLayout(max_parts(*di, D), RPAD, D).total;
 }
 
-extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
-                          const int64_t strides[6], int PS, const int32_t* block_tables, int MP,
-                          const int32_t* seq_lens, const int32_t* query_start_loc, int B, int KVH, int G, int D,
-                          int qlmax, float sm_scale, float v_scale, const float* gk, const float* gv, void* workspace,
-                          size_t workspace_bytes, int splits, void* out, void* stream) {
+static int decode_impl(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
+                       const int64_t strides[6], int PS, const int32_t* block_tables, int MP, const int32_t* seq_lens,
+                       const int32_t* query_start_loc, int B, int KVH, int G, int D, int qlmax, float sm_scale,
+                       float v_scale, const float* gk, const float* gv, void* workspace, size_t workspace_bytes,
+                       int splits, const float* signs, void* out, void* stream) {
   using namespace hkv;
   if (B < 0 || MP < 0) return HKV_ERR_RANGE;
   if (B == 0) return HKV_OK;
@@ -884,6 +925,9 @@ extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const 
   p.out = (__nv_bfloat16*)out;
   p.MP = MP; p.B = B; p.KVH = KVH; p.G = G; p.qlmax = qlmax; p.PS = PS;
   p.early_meta = g_early_metadata.load(std::memory_order_relaxed);
+  if (signs && ((uintptr_t)signs & 15)) return HKV_ERR_ALIGN;
+  p.signs = signs;
+  p.rot_scale = (float)(1.0 / sqrt((double)D));
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.v_scale = v_scale;
   cudaStream_t st = (cudaStream_t)stream;
@@ -908,6 +952,26 @@ extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const 
     }
   }
   return HKV_OK;
+}
+
+extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
+                          const int64_t strides[6], int PS, const int32_t* block_tables, int MP,
+                          const int32_t* seq_lens, const int32_t* query_start_loc, int B, int KVH, int G, int D,
+                          int qlmax, float sm_scale, float v_scale, const float* gk, const float* gv, void* workspace,
+                          size_t workspace_bytes, int splits, void* out, void* stream) {
+  return decode_impl(q, kd, ksf, vd, vsf, strides, PS, block_tables, MP, seq_lens, query_start_loc, B, KVH, G, D, qlmax,
+                     sm_scale, v_scale, gk, gv, workspace, workspace_bytes, splits, nullptr, out, stream);
+}
+
+extern "C" int hkv_decode_rot(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
+                              const int64_t strides[6], int PS, const int32_t* block_tables, int MP,
+                              const int32_t* seq_lens, const int32_t* query_start_loc, int B, int KVH, int G, int D,
+                              int qlmax, float sm_scale, float v_scale, const float* gk, const float* gv,
+                              void* workspace, size_t workspace_bytes, int splits, const float* signs, void* out,
+                              void* stream) {
+  if (B > 0 && !signs) return HKV_ERR_NULL;
+  return decode_impl(q, kd, ksf, vd, vsf, strides, PS, block_tables, MP, seq_lens, query_start_loc, B, KVH, G, D, qlmax,
+                     sm_scale, v_scale, gk, gv, workspace, workspace_bytes, splits, signs, out, stream);
 }
 
 extern "C" int hkv_combine(const void* workspace, size_t workspace_bytes, const int32_t* query_start_loc, int B,

@@ -13,6 +13,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
@@ -33,6 +34,8 @@ struct WriteParams {
   long long n_slots;
   const float* gk;
   const float* gv;
+  const float* signs;                              // +-1 per channel of the optional key rotation, or null
+  float rot_scale;                                 // head_dim^-0.5 rounded to fp32
   int PS, KVH;
 };
 
@@ -158,7 +161,12 @@ __device__ __forceinline__ void score(const float (&ax)[16], float sc, BlockCode
 // and stores 256 B contiguous. LPB = 4 (few tokens, latency matters): the four lanes of a quad read the same block,
 // lane k scores candidate k, the quad agrees on the winner with shuffles in candidate order (strict "<", so the
 // earliest candidate wins a tie, as in the reference) and every lane stores 4 of the 16 codes.
-template <int D, int SEARCH, int LPB>
+//
+// HAD = 1 (with LPB = 1): the keys are rotated first, k' = FWHT(k * signs) * head_dim^-0.5 in fp32 with the
+// reference's butterfly order (kv_fp4_ref.py:31-35, :55-87), and quantised from the fp32 result. The D / 16 lanes of
+// a key row sit side by side in a warp: stages h = 1 .. 8 run inside a lane, the others exchange with the lane
+// 1, 2, 4 (, 8) positions away. Values are never rotated.
+template <int D, int SEARCH, int LPB, int HAD>
 __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   constexpr int NB = D / 16;                      // blocks per row
   pdl_wait();                                     // inputs and the cache may come from the preceding launch
@@ -166,12 +174,18 @@ __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   const int n_blocks = 2 * p.KVH * NB;            // per token (a multiple of 16)
   const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LPB;
   const int cand = LPB == 4 ? (threadIdx.x & 3) : 0;
-  const long long t = gid / n_blocks;
-  if (t >= p.n_slots) return;                     // whole quads (gid is shared by a quad), whole warps when LPB == 4
+  long long t = gid / n_blocks;
   const int bid = (int)(gid - t * n_blocks);
+  // With LPB == 4 a warp holds one token's blocks, so this exit is warp-uniform. With the rotation the lanes of a warp
+  // exchange values, so lanes past the end stay (on the last token's data) and only skip the stores.
+  const bool in_range = t < p.n_slots;
+  if (!in_range) {
+    if (!HAD) return;
+    t = p.n_slots - 1;
+  }
   const long long slot = p.slots[t];
   // a quad shares its token, so `active` is uniform in a quad; inactive lanes still take part in the shuffles below
-  const bool active = slot >= 0;
+  const bool active = in_range && slot >= 0;
   long long page = 0, pos = 0;
   if (active) {
     if ((p.PS & (p.PS - 1)) == 0) {
@@ -197,6 +211,44 @@ __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   for (int i = 0; i < 8; ++i) {
     x[2 * i] = __uint_as_float(ws[i] << 16);
     x[2 * i + 1] = __uint_as_float(ws[i] & 0xffff0000u);
+  }
+  if (HAD) {
+    // every lane of the warp runs the exchange (value rows too, whose results are dropped)
+    float y[16];
+    const float4* sg = reinterpret_cast<const float4*>(p.signs + blk * 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 s4 = __ldg(sg + i);
+      y[4 * i] = __fmul_rn(x[4 * i], s4.x);
+      y[4 * i + 1] = __fmul_rn(x[4 * i + 1], s4.y);
+      y[4 * i + 2] = __fmul_rn(x[4 * i + 2], s4.z);
+      y[4 * i + 3] = __fmul_rn(x[4 * i + 3], s4.w);
+    }
+#pragma unroll
+    for (int hh = 1; hh < 16; hh *= 2)
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if ((i & hh) == 0) {
+          const float a = y[i], b = y[i + hh];
+          y[i] = __fadd_rn(a, b);
+          y[i + hh] = __fsub_rn(a, b);
+        }
+#pragma unroll
+    for (int m = 1; m < NB; m *= 2) {                // stage h = 16 m: partner block = blk ^ m
+      const bool upper = (blk & m) != 0;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float o = __shfl_xor_sync(0xffffffffu, y[i], m);
+        y[i] = upper ? __fsub_rn(o, y[i]) : __fadd_rn(y[i], o);
+      }
+    }
+    if (side == 0) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) x[i] = __fmul_rn(y[i], p.rot_scale);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
     ax[2 * i] = fabsf(x[2 * i]);
     ax[2 * i + 1] = fabsf(x[2 * i + 1]);
     amax = fmaxf(amax, fmaxf(ax[2 * i], ax[2 * i + 1]));
@@ -297,10 +349,10 @@ int record_cuda(cudaError_t e) {
 }
 }  // namespace hkv
 
-extern "C" int hkv_write(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1,
-                         void* kd, void* ksf, void* vd, void* vsf, const int64_t strides[6], int PS,
-                         const int64_t* slots, int64_t n_slots, const float* gk, const float* gv, int KVH, int D,
-                         int search, void* stream) {
+static int write_impl(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1, void* kd,
+                      void* ksf, void* vd, void* vsf, const int64_t strides[6], int PS, const int64_t* slots,
+                      int64_t n_slots, const float* gk, const float* gv, int KVH, int D, int search,
+                      const float* signs, void* stream) {
   using namespace hkv;
   if (n_slots < 0) return HKV_ERR_RANGE;
   if (n_slots == 0) return HKV_OK;
@@ -322,20 +374,44 @@ extern "C" int hkv_write(const void* key, const void* val, int64_t ks0, int64_t 
   p.slots = (const long long*)slots;
   p.n_slots = n_slots;
   p.gk = gk; p.gv = gv; p.PS = PS; p.KVH = KVH;
-  // lanes: one per (token, block) for prefill-sized launches, a quad per (token, block) for few tokens (decode appends)
-  const int lpb = n_slots <= 4096 ? 4 : 1;
+  p.signs = signs;
+  p.rot_scale = (float)(1.0 / sqrt((double)D));
+  if (signs && ((uintptr_t)signs & 15)) return HKV_ERR_ALIGN;
+  // lanes: one per (token, block) for prefill-sized launches and whenever the keys are rotated, a quad per
+  // (token, block) for few tokens (decode appends)
+  const int lpb = (n_slots <= 4096 && !signs) ? 4 : 1;
   const int threads = 256;
   const long long lanes = n_slots * (2ll * KVH * (D / 16)) * lpb;
   const long long blocks = (lanes + threads - 1) / threads;
   if (blocks > 0x7fffffffll) return HKV_ERR_RANGE;
   cudaStream_t st = (cudaStream_t)stream;
   void (*k)(const WriteParams);
-  if (D == 128) {
-    k = lpb == 1 ? (search ? write_kernel<128, 1, 1> : write_kernel<128, 0, 1>)
-                 : (search ? write_kernel<128, 1, 4> : write_kernel<128, 0, 4>);
+  if (signs) {
+    k = D == 128 ? (search ? write_kernel<128, 1, 1, 1> : write_kernel<128, 0, 1, 1>)
+                 : (search ? write_kernel<256, 1, 1, 1> : write_kernel<256, 0, 1, 1>);
+  } else if (D == 128) {
+    k = lpb == 1 ? (search ? write_kernel<128, 1, 1, 0> : write_kernel<128, 0, 1, 0>)
+                 : (search ? write_kernel<128, 1, 4, 0> : write_kernel<128, 0, 4, 0>);
   } else {
-    k = lpb == 1 ? (search ? write_kernel<256, 1, 1> : write_kernel<256, 0, 1>)
-                 : (search ? write_kernel<256, 1, 4> : write_kernel<256, 0, 4>);
+    k = lpb == 1 ? (search ? write_kernel<256, 1, 1, 0> : write_kernel<256, 0, 1, 0>)
+                 : (search ? write_kernel<256, 1, 4, 0> : write_kernel<256, 0, 4, 0>);
   }
   return record_cuda(launch_pdl(k, dim3((unsigned)blocks), dim3(threads), 0, st, p));
+}
+
+extern "C" int hkv_write(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1,
+                         void* kd, void* ksf, void* vd, void* vsf, const int64_t strides[6], int PS,
+                         const int64_t* slots, int64_t n_slots, const float* gk, const float* gv, int KVH, int D,
+                         int search, void* stream) {
+  return write_impl(key, val, ks0, ks1, vs0, vs1, kd, ksf, vd, vsf, strides, PS, slots, n_slots, gk, gv, KVH, D,
+                    search, nullptr, stream);
+}
+
+extern "C" int hkv_write_rot(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1,
+                             void* kd, void* ksf, void* vd, void* vsf, const int64_t strides[6], int PS,
+                             const int64_t* slots, int64_t n_slots, const float* gk, const float* gv, int KVH, int D,
+                             int search, const float* signs, void* stream) {
+  if (!signs) return HKV_ERR_NULL;
+  return write_impl(key, val, ks0, ks1, vs0, vs1, kd, ksf, vd, vsf, strides, PS, slots, n_slots, gk, gv, KVH, D,
+                    search, signs, stream);
 }

@@ -56,13 +56,48 @@ def alloc_workspace(B: int, KVH: int, G: int, D: int, qlmax: int = 1, device="cu
         return torch.zeros(workspace_bytes(B, KVH, G, D, qlmax), dtype=torch.uint8, device=device)
 
 
+SIGN_SEED = 0x6B7634              # the reference's seed of the rotation's sign vector (kv_fp4_ref.py:49)
+
+
+def hadamard_signs(D: int, seed: int = SIGN_SEED, device=None) -> torch.Tensor:
+    """the reference's fixed random +-1 per channel (kv_fp4_ref.py:57-60): the same vector must serve q and k"""
+    g = torch.Generator().manual_seed(seed)
+    s = (torch.randint(0, 2, (D,), generator=g) * 2 - 1).to(torch.float32)
+    return s if device is None else s.to(device)
+
+
+def rotate(x: torch.Tensor, signs: torch.Tensor) -> torch.Tensor:
+    """fp32 FWHT(x * signs) * D^-0.5 over the last dimension, butterflies in the stage order h = 1, 2, .., D / 2
+    (kv_fp4_ref.py:63-87). A torch helper for eager paths (prefill queries); the kernels rotate in registers."""
+    D = x.shape[-1]
+    y = (x.float() * signs.to(x.device, torch.float32)).reshape(-1, D)
+    h = 1
+    while h < D:
+        v = y.view(-1, D // (2 * h), 2, h)
+        y = torch.stack((v[:, :, 0] + v[:, :, 1], v[:, :, 0] - v[:, :, 1]), dim=2).reshape(-1, D)
+        h *= 2
+    scale = float(torch.tensor(1.0 / (D ** 0.5), dtype=torch.float32))
+    return (y * scale).view(x.shape)
+
+
+def _check_signs(signs, D):
+    if signs is None:
+        return
+    _need_cuda(signs)
+    if signs.dtype != torch.float32 or signs.shape != (D,) or not signs.is_contiguous():
+        raise TypeError("signs must be a contiguous fp32 tensor of head_dim entries")
+
+
 def write(key, value, flat, strides, PS, slot_mapping, gk, gv, search=True, signs=None, k8=False):
     """key / value (NT, KVH, D) bf16 views (any token / head strides, last dim contiguous); slot_mapping (NSL,) int64,
     slot < 0 skipped, tokens beyond NSL untouched; flat / strides from flat_views; gk / gv (KVH,) fp32.
-    Bit-exact to the reference's write_reference (kv_fp4_ref.py:233-245). Signature of kv_fp4_serving.py:994."""
-    if signs is not None or k8:
-        raise NotImplementedError("key rotation and the K8V4 slot are not built")
+    signs (D,) fp32 of +-1 on the device: the keys are rotated (FWHT(k * signs) * D^-0.5 in fp32) before they are
+    quantised. Bit-exact to the reference's write_reference (kv_fp4_ref.py:233-245). Signature of
+    kv_fp4_serving.py:994."""
+    if k8:
+        raise NotImplementedError("the K8V4 slot is not built")
     _need_cuda(key, value, slot_mapping, gk, gv, *flat)
+    _check_signs(signs, key.shape[2])
     if key.dtype != torch.bfloat16 or value.dtype != torch.bfloat16:
         raise TypeError("key / value must be bf16")
     if key.stride(-1) != 1 or value.stride(-1) != 1:
@@ -74,11 +109,14 @@ def write(key, value, flat, strides, PS, slot_mapping, gk, gv, search=True, sign
     KVH, D = key.shape[1], key.shape[2]
     kd, ksf, vd, vsf = flat
     st = (C.c_int64 * 6)(*strides)
+    args = (_ptr(key), _ptr(value), key.stride(0), key.stride(1), value.stride(0), value.stride(1), _ptr(kd), _ptr(ksf),
+            _ptr(vd), _ptr(vsf), st, int(PS), _ptr(slot_mapping), slot_mapping.shape[0], _ptr(gk), _ptr(gv), KVH, D,
+            int(bool(search)))
     with torch.cuda.device(key.device):
-        rc = _lib.load().hkv_write(_ptr(key), _ptr(value), key.stride(0), key.stride(1), value.stride(0),
-                                   value.stride(1), _ptr(kd), _ptr(ksf), _ptr(vd), _ptr(vsf), st, int(PS),
-                                   _ptr(slot_mapping), slot_mapping.shape[0], _ptr(gk), _ptr(gv), KVH, D,
-                                   int(bool(search)), _stream())
+        if signs is None:
+            rc = _lib.load().hkv_write(*args, _stream())
+        else:
+            rc = _lib.load().hkv_write_rot(*args, _ptr(signs), _stream())
     _lib.check(rc, "hkv_write")
 
 
@@ -89,10 +127,13 @@ def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_
     int32; out (>= NT, HQ, D) bf16, rows of requests without (or with more than qlmax) query tokens are left
     untouched; workspace from alloc_workspace. out = softmax(q k^T * bmm1_scale * gk) v * gv * bmm2_scale.
     `splits` bounds the number of stream partitions to B * KVH * splits; the tuning arguments of the reference
-    (nst, ncw, min_chunk, tw) are accepted and ignored. Signature of kv_fp4_serving.py:894-895."""
-    if signs is not None or k8:
-        raise NotImplementedError("key rotation and the K8V4 slot are not built")
+    (nst, ncw, min_chunk, tw) are accepted and ignored. signs (D,) fp32 of +-1 on the device: the keys in the cache
+    were written rotated, and the kernel rotates the UNROTATED query it is given the same way.
+    Signature of kv_fp4_serving.py:894-895."""
+    if k8:
+        raise NotImplementedError("the K8V4 slot is not built")
     _need_cuda(query, block_tables, seq_lens, query_start_loc, gk, gv, out, workspace, *flat)
+    _check_signs(signs, query.shape[2])
     if query.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise TypeError("query / out must be bf16")
     if not query.is_contiguous() or not out.is_contiguous():
@@ -111,9 +152,10 @@ def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_
     L = _lib.load()
     with torch.cuda.device(query.device):
         s = _stream()
-        rc = L.hkv_decode(_ptr(query), _ptr(kd), _ptr(ksf), _ptr(vd), _ptr(vsf), st, int(PS), _ptr(block_tables), MP,
-                          _ptr(seq_lens), _ptr(query_start_loc), B, KVH, G, D, int(qlmax), float(bmm1_scale),
-                          float(bmm2_scale), _ptr(gk), _ptr(gv), _ptr(workspace), wsb, S, _ptr(out), s)
+        args = (_ptr(query), _ptr(kd), _ptr(ksf), _ptr(vd), _ptr(vsf), st, int(PS), _ptr(block_tables), MP,
+                _ptr(seq_lens), _ptr(query_start_loc), B, KVH, G, D, int(qlmax), float(bmm1_scale), float(bmm2_scale),
+                _ptr(gk), _ptr(gv), _ptr(workspace), wsb, S)
+        rc = L.hkv_decode(*args, _ptr(out), s) if signs is None else L.hkv_decode_rot(*args, _ptr(signs), _ptr(out), s)
         _lib.check(rc, "hkv_decode")
         if not _combine:                      # (benchmark only: time the decode kernel alone; `out` is incomplete)
             return out

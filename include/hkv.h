@@ -124,6 +124,27 @@ int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf, const voi
                        float v_scale, const float* gk, const float* gv, int splits, void* out, void* stream);
 
 /*
+ * The same two operations with the reference's optional key rotation (kv_fp4_ref.py:31-35, :55-92): `signs` is a
+ * fixed vector of +-1 per channel (fp32[D], 16-byte aligned; the reference's `hadamard_signs`).
+ *   hkv_write_rot  quantises k' = FWHT(k * signs) * D^-0.5, computed in fp32 with the reference's butterfly order, from
+ *                  the fp32 result (values are not rotated): bit-exact to `write_reference(..., signs=signs)`
+ *                  (kv_fp4_ref.py:233-241; `hz4::write_task<.., HAD = 1>` kv_fp4_serving.py:621-641).
+ *   hkv_decode_rot rotates every query row the same way inside the kernel, rounded once to bf16 like `rotate_q`
+ *                  (kv_fp4_ref.py:90-92; the fused rotation of kv_fp4_serving.py:146-189), so q' . k' = q . k and the
+ *                  model's math is unchanged. Followed by hkv_combine like hkv_decode.
+ * All other arguments as for hkv_write / hkv_decode.
+ */
+int hkv_write_rot(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1, void* kd,
+                  void* ksf, void* vd, void* vsf, const int64_t strides[6], int PS, const int64_t* slots,
+                  int64_t n_slots, const float* gk, const float* gv, int KVH, int D, int search, const float* signs,
+                  void* stream);
+int hkv_decode_rot(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
+                   const int64_t strides[6], int PS, const int32_t* block_tables, int MP, const int32_t* seq_lens,
+                   const int32_t* query_start_loc, int B, int KVH, int G, int D, int qlmax, float sm_scale,
+                   float v_scale, const float* gk, const float* gv, void* workspace, size_t workspace_bytes,
+                   int splits, const float* signs, void* out, void* stream);
+
+/*
  * Exact dequantisation of cached tokens into dense bf16 or fp16 rows (n_tokens, KVH, D), the input of a prefill
  * attention over a cached prefix: value = e2m1(code) * e4m3(block scale), WITHOUT the global scales gk / gv (the
  * product is exact in both output types; the caller folds the global scales into its softmax scale and its output).
