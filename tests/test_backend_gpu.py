@@ -102,3 +102,42 @@ def test_mixed_step_with_prefill_rows(KVH, G, D, PS):
     # relative L2, holds; the absolute error scales with the outputs, which reach the values' outliers here
     mx, mn, rl = errors(got[torch.from_numpy(~dec).to(dev)], want[~dec])
     assert rl <= 2.5e-3 and mn <= 2e-3 and mx <= 6e-2, (mx, mn, rl)
+
+
+def test_rotation_option_end_to_end(monkeypatch):
+    """HORIZON_KVFP4_HAD=1: do_kv_cache_update writes rotated keys, forward rotates the queries of decode rows inside the
+    kernel and of prefill rows in torch; both against fp64 attention of rotate_q(q) over the rotated cache"""
+    monkeypatch.setenv("HORIZON_KVFP4_HAD", "1")
+    from horizon_kernels_b200 import kernels as K
+    KVH, G, D, PS = 4, 4, 128, 16
+    lens, qls = [500, 90, 64], [1, 30, 1]
+    c = synth.paged_case(88, lens, KVH, G, D, PS, outliers=True, ql_list=qls)
+    dev = torch.device("cuda")
+    B, HQ, NT = len(lens), KVH * G, sum(qls)
+    kscale, vscale = 0.02, 1.0
+    layer = SimpleNamespace(_k_scale_float=kscale, _v_scale_float=vscale, layer_name="model.layers.1.self_attn.attn")
+    impl = BE.HorizonFp4Impl(HQ, D, D ** -0.5, num_kv_heads=KVH, kv_cache_dtype="nvfp4", max_num_seqs=8)
+    assert impl.had
+    kv_cache = Lt.alloc_cache(c["NP"], PS, KVH, D, device=dev, fill=0x7F)
+    impl.do_kv_cache_update(layer, bf16_tensor(c["key"]), bf16_tensor(c["val"]), kv_cache,
+                            torch.from_numpy(c["slots"]).to(dev))
+    lay = O.Layout.slots(PS, KVH, D)
+    gk, gv = np.full(KVH, kscale, np.float32), np.full(KVH, vscale, np.float32)
+    signs = K.hadamard_signs(D).numpy()
+    want = np.full(kv_cache.numel(), 0x7F, np.uint8)
+    O.write(c["key"], c["val"], want, lay, c["slots"], gk, gv, True, signs=signs)
+    assert np.array_equal(kv_cache.cpu().numpy().reshape(-1), want)
+    qsl = torch.from_numpy(c["qsl"])
+    cam = SimpleNamespace(num_reqs=B, num_actual_tokens=NT, query_start_loc=qsl.to(dev), query_start_loc_cpu=qsl,
+                          seq_lens=torch.from_numpy(c["seq_lens"]).to(dev),
+                          block_table_tensor=torch.from_numpy(c["bt"]).to(dev),
+                          slot_mapping=torch.zeros(NT, dtype=torch.int64, device=dev),
+                          seq_lens_cpu_upper_bound=torch.from_numpy(c["seq_lens"]))
+    meta = BE.HorizonFp4Builder().build(0, cam)
+    output = torch.zeros((NT, HQ * D), dtype=torch.bfloat16, device=dev)
+    impl.forward(layer, bf16_tensor(c["q"]).view(NT, HQ * D), None, None, kv_cache, meta, output)
+    ref, _ = O.attention(O.rotate_q(c["q"], signs), want, lay, c["bt"], c["seq_lens"], c["qsl"], KVH, D ** -0.5, gk,
+                         gv, 1.0)
+    from cases import errors
+    mx, mn, rl = errors(output.view(NT, HQ, D), ref)
+    assert rl <= 2.5e-3 and mn <= 2e-3 and mx <= 6e-2, (mx, mn, rl)
