@@ -60,6 +60,7 @@ struct DecodeParams {
   const float* signs;                                // +-1 per channel when the keys were written rotated, else null
   float rot_scale;                                   // head_dim^-0.5 rounded to fp32
   int row0;                                          // first query row (of the G * ql rows of a request and kv head) of this pass
+  int max_len;                                       // MP * PS, capped at INT_MAX
   int early_meta;                                    // seq_lens / query_start_loc are read before the launch dependency
   float scale_log2, v_scale;
 };
@@ -117,7 +118,8 @@ __device__ __forceinline__ ReqInfo load_req(const DecodeParams& p, int b) {
   int ql = __ldg(p.qsl + b + 1) - r.q0;
   ql = (ql < 0 || ql > p.qlmax || p.G * ql <= p.row0) ? 0 : ql;     // (no rows in this pass: the request is skipped)
   r.ql = ql;
-  r.L = ql > 0 ? max(__ldg(p.seq_lens + b), 0) : 0;
+  // (a length beyond the block table's reach is cut there, so that bad metadata can never read past a table row)
+  r.L = ql > 0 ? min(max(__ldg(p.seq_lens + b), 0), p.max_len) : 0;
   r.U = ql > 0 ? max(1, (r.L + (1 << LOG_UT) - 1) >> LOG_UT) : 0;
   return r;
 }
@@ -925,6 +927,7 @@ static int decode_impl(const void* q, const void* kd, const void* ksf, const voi
   p.out = (__nv_bfloat16*)out;
   p.MP = MP; p.B = B; p.KVH = KVH; p.G = G; p.qlmax = qlmax; p.PS = PS;
   p.early_meta = g_early_metadata.load(std::memory_order_relaxed);
+  p.max_len = (int)std::min<long long>((long long)MP * PS, 0x7fffffffll);
   if (signs && ((uintptr_t)signs & 15)) return HKV_ERR_ALIGN;
   p.signs = signs;
   p.rot_scale = (float)(1.0 / sqrt((double)D));

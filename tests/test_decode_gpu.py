@@ -219,6 +219,20 @@ def test_more_than_eight_query_rows(KVH, G, D, qls):
     assert_close(out2, ref, "splits 2")
 
 
+def test_length_beyond_the_block_table_is_cut_at_its_reach():
+    """seq_lens larger than MP * PS (bad metadata) must not read past the block-table row: the kernel uses MP * PS"""
+    c = build_decode_case(2460, [112, 64], 2, 4, 128, 16)
+    MP = c["bt"].shape[1]
+    full = dict(c, seq_lens=np.array([MP * 16, 64], np.int32), bt=c["bt"].copy())
+    if MP * 16 > 112:                                            # pages past the context: point them at page 0 (written)
+        full["bt"][0, 7:] = c["bt"][0, 0]
+    want, _ = gpu_decode(full)
+    bad = dict(full, seq_lens=np.array([1 << 30, 64], np.int32))
+    got, ws = gpu_decode(bad)
+    assert K.workspace_status(ws) == 0
+    assert torch.equal(got, want)
+
+
 def test_unsupported_shapes_raise():
     with pytest.raises(_lib.HkvError):
         K.alloc_workspace(1, 1, 65, 128, 1)                                # more than 64 query rows per kv head
