@@ -507,7 +507,8 @@ def main():
             "tokens_per_s_per_gpu": value / world,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_source": peak_src, "kernel": "hkv::decode_kernel",
-                         "algorithmic_bytes_per_launch": alg, "kernel_ms": dec_ms_avg},
+                         "algorithmic_bytes_per_launch": alg, "kernel_ms": dec_ms_avg,
+                         "frac_of_nominal_8tbs": achieved / 8000.0},
             "step_hbm_gbs": alg / (ms_step * 1e-3) / 1e9,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps},

@@ -124,13 +124,15 @@ def test_write_graph_replay():
         assert np.array_equal(cache.bytes(), first)
 
 
-def test_config3_fill_then_appends():
-    """quantize-on-write cache fill at reduced size (4096 prefill tokens, then 16 single-token appends for 128
-    sequences), every cache byte equal to the oracle's; then the full 32768-token prefill checked by a checksum of
-    per-page checksums against the oracle on a sample of pages"""
+@pytest.mark.parametrize("search", [True, False])
+def test_config3_fill_then_appends(search):
+    """BASELINE config 3 at full size: a prefill write of 32768 tokens x 8 kv heads x 128 into random pages, then 256
+    steps appending one token to each of 128 sequences (crossing page boundaries); every cache byte, canaries of the
+    untouched pages included, equal to the oracle's, with the scale search on and off"""
     KVH, D, PS = 8, 128, 16
-    NT, NSEQ, STEPS = 4096, 128, 16
-    NP = NT // PS + NSEQ * 2 + 8
+    NT, NSEQ, STEPS = 32768, 128, 256
+    app_pp = (STEPS + 9 + PS - 1) // PS                        # pages an appended sequence touches
+    NP = NT // PS + NSEQ * app_pp + 8
     kb, vb = kv_tokens(400, NT, KVH, D, "outlier")
     perm = synth.permutation(401, NP)
     pre_pages = perm[:NT // PS]
@@ -139,15 +141,19 @@ def test_config3_fill_then_appends():
     gv = np.full(KVH, synth.tensor_scale(vb), np.float32)
     cache = Cache(NP, PS, KVH, D, "hnd", fill=0xA5)
     want = np.full(cache.bytes().shape, 0xA5, np.uint8)
-    gpu_write(cache, bf16_tensor(kb), bf16_tensor(vb), dev_t(slots), dev_t(gk), dev_t(gv), True)
-    O.write(kb, vb, want, cache.olay, slots, gk, gv, True)
-    app_pages = perm[NT // PS:NT // PS + NSEQ * 2].reshape(NSEQ, 2)
+    gpu_write(cache, bf16_tensor(kb), bf16_tensor(vb), dev_t(slots), dev_t(gk), dev_t(gv), search)
+    O.write(kb, vb, want, cache.olay, slots, gk, gv, search)
+    app_pages = perm[NT // PS:NT // PS + NSEQ * app_pp].reshape(NSEQ, app_pp)
+    ak, av = kv_tokens(500, NSEQ * STEPS, KVH, D, "random")
+    ak, av = ak.reshape(STEPS, NSEQ, KVH, D), av.reshape(STEPS, NSEQ, KVH, D)
+    dk, dv, dgk, dgv = bf16_tensor(ak), bf16_tensor(av), dev_t(gk), dev_t(gv)
+    all_sl = []
     for step in range(STEPS):
-        ak, av = kv_tokens(500 + step, NSEQ, KVH, D, "random")
-        pos = 9 + step                                       # appends cross a page boundary at pos 16
+        pos = 9 + step
         sl = (app_pages[np.arange(NSEQ), pos // PS] * PS + pos % PS).astype(np.int64)
-        gpu_write(cache, bf16_tensor(ak), bf16_tensor(av), dev_t(sl), dev_t(gk), dev_t(gv), True)
-        O.write(ak, av, want, cache.olay, sl, gk, gv, True)
+        all_sl.append(sl)
+        gpu_write(cache, dk[step], dv[step], dev_t(sl), dgk, dgv, search)
+    O.write(ak.reshape(-1, KVH, D), av.reshape(-1, KVH, D), want, cache.olay, np.concatenate(all_sl), gk, gv, search)
     assert np.array_equal(cache.bytes(), want)
 
 
