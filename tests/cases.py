@@ -116,3 +116,28 @@ def assert_close(got, ref, what=""):
     mx, mn, rl = errors(got, ref)
     assert mx <= MAX_ABS and mn <= MEAN_ABS and rl <= REL_L2, (what, mx, mn, rl)
     return mx, mn, rl
+
+
+def unquantised_attention(c, sm=None):
+    """fp64 attention over the UNQUANTISED bf16 keys and values of a synth.paged_case (the "float64 oracle" column of
+    the reference's GPU gates, scripts/kernels/kvfp4/test_kvfp4_gpu.py:204-218): what the model would compute without a
+    4-bit cache. Token t of a request with ql query tokens and L cached tokens sees keys j < L - ql + t + 1."""
+    KVH, G, D = c["KVH"], c["G"], c["D"]
+    sm = D ** -0.5 if sm is None else sm
+    key, val, q = (O.bf16_to_f32(c[n]).astype(np.float64) for n in ("key", "val", "q"))
+    out = np.full(q.shape, np.nan)
+    t0 = 0
+    for b, L in enumerate(int(x) for x in c["seq_lens"]):
+        kb, vb = key[t0:t0 + L], val[t0:t0 + L]
+        t0 += L
+        q0, q1 = int(c["qsl"][b]), int(c["qsl"][b + 1])
+        for t in range(q1 - q0):
+            lim = L - (q1 - q0) + t + 1
+            if lim <= 0:
+                out[q0 + t] = 0.0
+                continue
+            for h in range(KVH):
+                s_ = (q[q0 + t, h * G:(h + 1) * G] @ kb[:lim, h].T) * sm
+                p_ = np.exp(s_ - s_.max(axis=1, keepdims=True))
+                out[q0 + t, h * G:(h + 1) * G] = (p_ / p_.sum(axis=1, keepdims=True)) @ vb[:lim, h]
+    return out

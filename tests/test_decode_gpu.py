@@ -10,7 +10,8 @@ import pytest
 import torch
 
 import synth
-from cases import (Cache, assert_close, bf16_tensor, build_decode_case, errors, gpu_decode, oracle_decode)
+from cases import (Cache, assert_close, bf16_tensor, build_decode_case, errors, gpu_decode, oracle_decode,
+                   unquantised_attention)
 from horizon_kernels_b200 import kernels as K
 from horizon_kernels_b200 import _lib
 
@@ -152,6 +153,22 @@ def test_early_metadata_option_changes_nothing():
     finally:
         K.set_option(K.OPT_EARLY_METADATA, 0)
     assert_close(out0, ref)
+
+
+def test_error_against_unquantised_fp64_attention():
+    """the "float64 oracle" column: error of the whole 4-bit path (quantise, decode) against fp64 attention over the
+    unquantised bf16 K / V, config-0 shape (batch 4, 32 / 8 heads, head_dim 128, 2048 tokens, N(0,1) data, global scale
+    amax / (6 * 448)). The GPU result must not add error beyond the format's: it stays as close to the unquantised
+    truth as the reference's own fp64 attention over the same cache does."""
+    c = build_decode_case(2350, [2048] * 4, 8, 4, 128, 16, outliers=False)
+    out, _ = gpu_decode(c)
+    ref = oracle_decode(c)
+    true = unquantised_attention(c, c["sm"])
+    got = out.float().cpu().numpy().astype(np.float64)
+    e_gpu = np.linalg.norm(got - true) / np.linalg.norm(true)
+    e_ref = np.linalg.norm(ref - true) / np.linalg.norm(true)
+    print("relative L2 vs unquantised fp64 attention: gpu %.4f, fp64 attention over the cache %.4f" % (e_gpu, e_ref))
+    assert e_gpu <= e_ref * 1.02 + 1e-3 and e_gpu < 0.2
 
 
 def test_long_context_split_and_combine():

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import synth
-from cases import Cache, assert_close, bf16_tensor
+from cases import Cache, assert_close, bf16_tensor, unquantised_attention
 from horizon_kernels_b200 import kernels as K
 from oracle import kvfp4 as O
 
@@ -82,18 +82,6 @@ def test_rotated_decode_matches_oracle(KVH, G, D, qls):
     assert_close(out, ref)
     # the rotation leaves the model's math unchanged (q' . k' = q . k): the result stays close to fp64 attention over
     # the UNQUANTISED bf16 keys and values; what remains is the 4-bit quantisation error of this outlier-heavy case
-    key, val, q = (O.bf16_to_f32(c[n]).astype(np.float64) for n in ("key", "val", "q"))
-    got = out.float().cpu().numpy().astype(np.float64)
-    err, t0 = [], 0
-    for b, L in enumerate(lens):
-        kb, vb = key[t0:t0 + L], val[t0:t0 + L]
-        t0 += L
-        for t in range(qls[b]):
-            lim = L - qls[b] + t + 1
-            row = int(c["qsl"][b]) + t
-            for h in range(KVH):
-                s_ = (q[row, h * G:(h + 1) * G] @ kb[:lim, h].T) * sm
-                p_ = np.exp(s_ - s_.max(axis=1, keepdims=True))
-                o = (p_ / p_.sum(axis=1, keepdims=True)) @ vb[:lim, h]
-                err.append(np.abs(got[row, h * G:(h + 1) * G] - o).mean())
+    true = unquantised_attention(c, sm)
+    err = np.abs(out.float().cpu().numpy().astype(np.float64) - true)
     assert np.mean(err) < 0.25, np.mean(err)
