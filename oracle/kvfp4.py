@@ -16,7 +16,7 @@ _lib = None
 
 class _CLayout(C.Structure):
     _fields_ = [(n, C.c_longlong) for n in ("kd", "ksf", "vd", "vsf", "dsp", "dst", "dsh", "ssp", "sst", "ssh")] + \
-               [("PS", C.c_int)]
+               [("PS", C.c_int), ("k8", C.c_int)]
 
 
 @dataclass
@@ -33,6 +33,7 @@ class Layout:
     sst: int
     ssh: int
     PS: int
+    k8: int = 0
 
     @staticmethod
     def region(PS: int, KVH: int, D: int) -> "Layout":
@@ -56,9 +57,17 @@ class Layout:
             st, sh = slot, PS * slot
         return Layout(0, dd, KVH * sh, KVH * sh + dd, page, st, sh, page, st, sh, PS)
 
+    @staticmethod
+    def k8_slots(PS: int, KVH: int, D: int) -> "Layout":
+        """K8V4 (kv_fp4_ref.py:283-293): logical (pages, KVH, PS, slot) with slot = [D e4m3 key bytes | D/2 value codes
+        | D/16 value scales] (400 bytes at head_dim 256), heads outermost inside a page"""
+        slot = D + D // 2 + D // 16
+        page = KVH * PS * slot
+        return Layout(0, 0, D, D + D // 2, page, slot, PS * slot, page, slot, PS * slot, PS, 1)
+
     def c(self) -> _CLayout:
         return _CLayout(self.kd, self.ksf, self.vd, self.vsf, self.dsp, self.dst, self.dsh, self.ssp, self.sst,
-                        self.ssh, self.PS)
+                        self.ssh, self.PS, self.k8)
 
     def strides(self):
         return (self.dsp, self.dst, self.dsh, self.ssp, self.sst, self.ssh)

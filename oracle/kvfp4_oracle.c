@@ -188,7 +188,16 @@ typedef struct {
   long long dsp, dst, dsh;             /* data strides: page, position, head */
   long long ssp, sst, ssh;             /* scale strides */
   int PS;
+  int k8;                              /* 1: K8V4 slot (kv_fp4_ref.py:283-321): keys are D signed e4m3 bytes at kd (no
+                                          block scales, ksf unused), values stay e2m1 codes + e4m3 block scales */
 } hkvo_layout;
+
+/* fp8_encode_signed (kv_fp4_ref.py:296-298): fp32 -> e4m3fn byte, round to nearest even, saturating to +-448; the sign
+ * bit survives for -0.0 and for negative values that round to zero */
+static uint8_t e4m3_encode_signed(float x) {
+  return (uint8_t)((signbit(x) ? 0x80 : 0) | hkvo_e4m3_encode(fabsf(x)));
+}
+static double e4m3_decode_signed(uint8_t b) { return (b & 0x80 ? -1.0 : 1.0) * hkvo_e4m3_decode(b & 0x7f); }
 
 /* write_reference (kv_fp4_ref.py:233-245): key/value (NT, KVH, D) bf16 with element strides (token, head), slot < 0
  * skipped, one global scale per kv head and side. signs != NULL: the keys are rotated first (hkvo_rotate_row) and
@@ -210,6 +219,10 @@ void hkvo_write_rot(const uint16_t* key, const uint16_t* val, long long ks0, lon
         uint8_t* ds = cache + (side ? lay->vsf : lay->ksf) + p * lay->ssp + o * lay->sst + h * lay->ssh;
         float g = side ? gv[h] : gk[h];
         for (int i = 0; i < D; ++i) row[i] = bf16_f32(src[i]);
+        if (lay->k8 && side == 0) {                    /* write_reference_k8 (kv_fp4_ref.py:301-311): e4m3(k / gk) */
+          for (int i = 0; i < D; ++i) { volatile float y = row[i] / g; dd[i] = e4m3_encode_signed(y); }
+          continue;
+        }
         if (signs && side == 0) hkvo_rotate_row(row, signs, D, rot_scale, row);
         for (int b = 0; b < nb; ++b) hkvo_quantize_block(row + b * 16, g, search, dd + b * 8, ds + b);
       }
@@ -244,6 +257,10 @@ long long hkvo_attention(const uint16_t* q, const uint8_t* cache, const hkvo_lay
           const uint8_t* dd = cache + (side ? lay->vd : lay->kd) + page * lay->dsp + pos * lay->dst + h * lay->dsh;
           const uint8_t* ds = cache + (side ? lay->vsf : lay->ksf) + page * lay->ssp + pos * lay->sst + h * lay->ssh;
           double* dst = (side ? V : K) + (size_t)j * D;
+          if (lay->k8 && side == 0) {                  /* gather_k8 (kv_fp4_ref.py:314-321) */
+            for (int i = 0; i < D; ++i) dst[i] = e4m3_decode_signed(dd[i]);
+            continue;
+          }
           for (int bb = 0; bb < nb; ++bb) {
             double s = hkvo_e4m3_decode(ds[bb]);
             for (int i = 0; i < 8; ++i) {

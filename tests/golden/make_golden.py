@@ -200,6 +200,40 @@ def rotation_cases(R):
     return out
 
 
+def k8_cases(R):
+    """the K8V4 slot (FP8 keys + FP4 values, 400 bytes at head_dim 256): write_reference_k8's cache bytes and fp64
+    attention over gather_k8's dequantised keys and values (the arithmetic of attention_reference)"""
+    KVH, G, D, PS = 2, 4, 256, 16
+    lens = [70, 16, 301]
+    c = synth.paged_case(800, lens, KVH, G, D, PS, outliers=True, ql_list=[1, 2, 1])
+    NP = c["NP"]
+    gk = np.array([0.05, 0.11], np.float32)
+    gv = np.array([0.01, 0.02], np.float32)
+    out = {"geom": np.array([KVH, G, D, PS, NP], np.int64), "gk": gk, "gv": gv}
+    out.update({k: c[k] for k in ("key", "val", "q", "bt", "slots", "seq_lens", "qsl")})
+    sm = D ** -0.5
+    for search in (0, 1):
+        cache = torch.full((NP, KVH, PS, R.K8_SLOT), 0xA5, dtype=torch.uint8)
+        views = R.split_views_k8(cache)
+        R.write_reference_k8(bf16(c["key"]), bf16(c["val"]), views, torch.from_numpy(c["slots"]),
+                             torch.from_numpy(gk), torch.from_numpy(gv), bool(search))
+        out[f"cache_s{search}"] = cache.numpy().reshape(-1)
+    q = bf16(c["q"]).double()
+    ref = torch.zeros(q.shape, dtype=torch.float64)
+    gk64, gv64 = torch.from_numpy(gk).double().view(KVH, 1, 1), torch.from_numpy(gv).double().view(1, KVH, 1)
+    for b, L in enumerate(lens):
+        K_, V_ = R.gather_k8(views, torch.from_numpy(c["bt"][b]), L)
+        q0, q1 = int(c["qsl"][b]), int(c["qsl"][b + 1])
+        for t in range(q1 - q0):
+            lim = L - (q1 - q0) + t + 1
+            qq = q[q0 + t].view(KVH, G, D)
+            s_ = torch.einsum("hgd,lhd->hgl", qq, K_[:lim]) * gk64 * sm
+            p_ = torch.softmax(s_, dim=-1)
+            ref[q0 + t] = torch.einsum("hgl,lhd->hgd", p_, V_[:lim] * gv64).reshape(KVH * G, D)
+    out["ref"] = ref.numpy()
+    return out
+
+
 def main():
     root = sys.argv[1]
     R = load_ref(root)
@@ -209,7 +243,8 @@ def main():
     np.savez_compressed(os.path.join(HERE, "attention.npz"), **attention_cases(R))
     np.savez_compressed(os.path.join(HERE, "config0.npz"), **config0(R))
     np.savez_compressed(os.path.join(HERE, "rotation.npz"), **rotation_cases(R))
-    for f in ("quant.npz", "write.npz", "attention.npz", "config0.npz", "rotation.npz"):
+    np.savez_compressed(os.path.join(HERE, "k8v4.npz"), **k8_cases(R))
+    for f in ("quant.npz", "write.npz", "attention.npz", "config0.npz", "rotation.npz", "k8v4.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
 
