@@ -70,6 +70,9 @@ struct DecodeParams {
 //             outermost inside a page): one bulk copy of 16 * slot bytes per 16 tokens and side
 //   LAYOUT 1  code rows back to back, then the scale rows (the page-region layout of the reference's torch oracle):
 //             two bulk copies per 16 tokens and side
+//   LAYOUT 2  the K8V4 slot (head_dim 256; kv_fp4_ref.py:283-293): token rows of [D signed E4M3 key bytes | D/2 value
+//             codes | D/16 value scales], heads outermost: keys and values of 16 tokens are ONE bulk copy of
+//             16 * 400 bytes; the stage holds those rows as they are
 template <int D, int LAYOUT>
 struct Geo {
   static constexpr int SD = D / 2, SS = D / 16, SLOT = SD + SS;
@@ -80,14 +83,18 @@ struct Geo {
 #define HKV_MINB128 3
 #endif
 
-  static constexpr int NS = D == 128 ? HKV_NS128 : 4;  // stages per warp
+  static constexpr int NS = D == 128 ? HKV_NS128 : LAYOUT == 2 ? 3 : 4;   // stages per warp
   static constexpr int MINB = D == 128 ? HKV_MINB128 : 2;   // CTAs per SM the register budget is sized for
+  static constexpr bool K8 = LAYOUT == 2;
+  static constexpr int SLOT8 = D + SD + SS;            // K8V4 slot: 400 bytes at head_dim 256
   static constexpr int TILE = UT * SLOT;               // bytes of one (head, side) tile of a unit
-  static constexpr int STAGE = 2 * TILE;
-  static constexpr int ROW = LAYOUT == 0 ? SLOT : SD;  // byte stride between code rows in shared memory
-  static constexpr int SD_ROW = ROW;                   // .. and between the code rows of one head in the cache
-  static constexpr int SF_BASE = LAYOUT == 0 ? SD : UT * SD;
-  static constexpr int SF_ROW = LAYOUT == 0 ? SLOT : SS;
+  static constexpr int STAGE = K8 ? UT * SLOT8 : 2 * TILE;
+  static constexpr int ROW = K8 ? SLOT8 : LAYOUT == 0 ? SLOT : SD;   // byte stride between token rows in shared memory
+  static constexpr int SD_ROW = ROW;                   // .. and between the rows of one head in the cache
+  static constexpr int KB = K8 ? 16 : 8;               // bytes of one 16-channel key block
+  static constexpr int V_BASE = K8 ? D : TILE;         // first value byte of the stage (of row 0)
+  static constexpr int SF_BASE = LAYOUT == 1 ? UT * SD : SD;        // value / key scales behind their side's codes
+  static constexpr int SF_ROW = K8 ? SLOT8 : LAYOUT == 0 ? SLOT : SS;
   static constexpr int KS = D / 16;                    // k-steps of K Q^T == mma tiles of V^T P^T (per 16 tokens)
   static constexpr int NBL = D / 64;                   // 16-channel blocks of one key row held by one lane
   static constexpr int NH = D / 128;                   // 16-channel blocks of one value row held by one lane
@@ -277,8 +284,8 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   uint32_t ring_a = smem_u32(ring + w * NS * Gm::STAGE), bars_a = smem_u32(bars + w * NS);
   const int r0 = Gm::tok(g), r1 = Gm::tok(g + 8);
   const int t00 = Gm::tok(2 * c);
-  uint32_t koff_d = r0 * Gm::ROW + 8 * Gm::kblk(c, 0), koff_s = Gm::SF_BASE + r0 * Gm::SF_ROW + Gm::kblk(c, 0);
-  uint32_t voff_d = Gm::TILE + t00 * Gm::ROW + 8 * g, voff_s = Gm::TILE + Gm::SF_BASE + t00 * Gm::SF_ROW + g;
+  uint32_t koff_d = r0 * Gm::ROW + Gm::KB * Gm::kblk(c, 0), koff_s = Gm::SF_BASE + r0 * Gm::SF_ROW + Gm::kblk(c, 0);
+  uint32_t voff_d = Gm::V_BASE + t00 * Gm::ROW + 8 * g, voff_s = Gm::V_BASE + Gm::SF_BASE + t00 * Gm::SF_ROW + g;
   asm volatile("" : "+r"(ring_a), "+r"(bars_a), "+r"(koff_d), "+r"(koff_s), "+r"(voff_d), "+r"(voff_s));
   constexpr int KR1 = Gm::tok(8) - Gm::tok(0);                            // r1 - r0 (the same for every g)
   constexpr int VR01 = Gm::tok(1) - Gm::tok(0), VR10 = Gm::tok(8) - Gm::tok(0),
@@ -345,7 +352,9 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
           if (bi < nb) {
             const unsigned pos0 = (unsigned)(tok0 + 16 * bi) & (unsigned)(p.PS - 1);
             const unsigned long long doff = (unsigned long long)(unsigned)page[bi] * p.dsp + pos0 * (unsigned)Gm::SD_ROW;
-            if (LAYOUT == 0) {
+            if (LAYOUT == 2) {
+              bulk_g2s_u32(st + bi * (16 * Gm::SLOT8), f_k + doff, 16 * Gm::SLOT8, bar);
+            } else if (LAYOUT == 0) {
               bulk_g2s_u32(st + bi * (16 * Gm::SLOT), f_k + doff, 16 * Gm::SLOT, bar);
               bulk_g2s_u32(st + bi * (16 * Gm::SLOT) + Gm::TILE, f_v + doff, 16 * Gm::SLOT, bar);
             } else {
@@ -517,6 +526,25 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
           float sa[Gm::NCH][4];
 #pragma unroll
           for (int i = 0; i < Gm::NCH; ++i) sa[i][0] = sa[i][1] = sa[i][2] = sa[i][3] = 0.0f;
+          if (Gm::K8) {
+            // FP8 keys: 16 bytes per block and row, no block scale (the global scale is part of `sc`)
+            const int dk8 = bi * 16 * Gm::ROW;
+#pragma unroll
+            for (int u = 0; u < Gm::NBL; ++u) {
+              const uint4 a = lds128(kd_ + dk8 + 16 * u), b = lds128(kd_ + dk8 + KR1 * Gm::ROW + 16 * u);
+              const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {           // k-step v of the block: channels 4v .. 4v+3 of rows r0, r1
+                uint32_t a0, a2, a1, a3;
+                e4m3x4_to_f16x2(wa[v], a0, a2);
+                e4m3x4_to_f16x2(wb[v], a1, a3);
+                mma_f16(sa[v & (Gm::NCH - 1)], a0, a1, a2, a3, qa[4 * u + v][0], qa[4 * u + v][1]);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x[bi][i] = Gm::NCH == 2 ? sa[0][i] + sa[Gm::NCH - 1][i] : sa[0][i];
+            continue;
+          }
           // codes and scales of this lane's NBL adjacent key blocks of rows r0 and r1
           const int dk = bi * 16 * Gm::ROW, sk = bi * 16 * Gm::SF_ROW;
           uint2 w0[Gm::NBL], w1[Gm::NBL];
@@ -574,7 +602,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
           // rows past the context hold arbitrary bytes: their scores become -inf below, and their value scales are
           // set to zero here, in shared memory, so that the value product needs no masking code
           if (lane < UT && tbase + lane >= L) {
-            const uint32_t a = st + Gm::TILE + Gm::SF_BASE + lane * Gm::SF_ROW;
+            const uint32_t a = st + Gm::V_BASE + Gm::SF_BASE + lane * Gm::SF_ROW;
 #pragma unroll
             for (int i = 0; i < Gm::SS; i += 8) sts64_zero(a + i);
             fence_proxy_async();                      // the stage's next bulk copy overwrites these bytes
@@ -825,7 +853,7 @@ int record_cuda(cudaError_t e);
 
 struct DeviceInfo {
   int sms = 0;
-  int ctas_per_sm[2][2] = {{0, 0}, {0, 0}};          // [D == 256][LAYOUT]
+  int ctas_per_sm[2][3] = {{0, 0, 0}, {0, 0, 0}};    // [D == 256][LAYOUT]
   bool ready = false;
 };
 static DeviceInfo g_dev[64];
@@ -852,6 +880,7 @@ static int device_info(DeviceInfo** out) {
     if ((e = setup_variant<128, 1>(di.ctas_per_sm[0][1])) != cudaSuccess) return record_cuda(e);
     if ((e = setup_variant<256, 0>(di.ctas_per_sm[1][0])) != cudaSuccess) return record_cuda(e);
     if ((e = setup_variant<256, 1>(di.ctas_per_sm[1][1])) != cudaSuccess) return record_cuda(e);
+    if ((e = setup_variant<256, 2>(di.ctas_per_sm[1][2])) != cudaSuccess) return record_cuda(e);
     di.ready = true;
   }
   *out = &di;
@@ -861,7 +890,7 @@ static int device_info(DeviceInfo** out) {
 // upper bound of partitions for any layout of this head_dim on this device
 static int max_parts(const DeviceInfo& di, int D) {
   const int i = D == 256;
-  return di.sms * max(1, max(di.ctas_per_sm[i][0], di.ctas_per_sm[i][1]));
+  return di.sms * max(1, max(di.ctas_per_sm[i][0], max(di.ctas_per_sm[i][1], di.ctas_per_sm[i][2])));
 }
 
 }  // namespace hkv
@@ -878,7 +907,7 @@ static int decode_impl(const void* q, const void* kd, const void* ksf, const voi
                        const int64_t strides[6], int PS, const int32_t* block_tables, int MP, const int32_t* seq_lens,
                        const int32_t* query_start_loc, int B, int KVH, int G, int D, int qlmax, float sm_scale,
                        float v_scale, const float* gk, const float* gv, void* workspace, size_t workspace_bytes,
-                       int splits, const float* signs, void* out, void* stream) {
+                       int splits, const float* signs, int k8, void* out, void* stream) {
   using namespace hkv;
   if (B < 0 || MP < 0) return HKV_ERR_RANGE;
   if (B == 0) return HKV_OK;
@@ -895,7 +924,15 @@ static int decode_impl(const void* q, const void* kd, const void* ksf, const voi
   const int64_t dsp = strides[0], dst = strides[1], dsh = strides[2], ssp = strides[3], sst = strides[4],
                 ssh = strides[5];
   int layout;
-  if (dst == SLOT && sst == SLOT && dsp == ssp && dsh == ssh && (const uint8_t*)ksf == (const uint8_t*)kd + SD &&
+  if (k8) {
+    // K8V4 slot: [D key bytes | D/2 value codes | D/16 value scales] per token, heads outermost (head_dim 256 only)
+    const int SLOT8 = D + SD + SS;
+    if (D != 256 || signs) return HKV_ERR_UNSUPPORTED;
+    if (dst != SLOT8 || sst != SLOT8 || dsp != ssp || dsh != ssh || (const uint8_t*)vd != (const uint8_t*)kd + D ||
+        (const uint8_t*)vsf != (const uint8_t*)vd + SD)
+      return HKV_ERR_UNSUPPORTED;
+    layout = 2;
+  } else if (dst == SLOT && sst == SLOT && dsp == ssp && dsh == ssh && (const uint8_t*)ksf == (const uint8_t*)kd + SD &&
       (const uint8_t*)vsf == (const uint8_t*)vd + SD)
     layout = 0;
   else if (dst == SD && sst == SS)
@@ -935,9 +972,11 @@ static int decode_impl(const void* q, const void* kd, const void* ksf, const voi
   p.v_scale = v_scale;
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned grid = (unsigned)n_parts;
-  void (*k)(const DecodeParams) = D == 128 ? (layout == 0 ? decode_kernel<128, 0> : decode_kernel<128, 1>)
-                                           : (layout == 0 ? decode_kernel<256, 0> : decode_kernel<256, 1>);
-  const size_t smem_bytes = D == 128 ? (size_t)Smem<128, 0>::TOTAL : (size_t)Smem<256, 0>::TOTAL;
+  void (*k)(const DecodeParams) =
+      D == 128 ? (layout == 0 ? decode_kernel<128, 0> : decode_kernel<128, 1>)
+               : (layout == 0 ? decode_kernel<256, 0> : layout == 1 ? decode_kernel<256, 1> : decode_kernel<256, 2>);
+  const size_t smem_bytes = D == 128 ? (size_t)Smem<128, 0>::TOTAL
+                                     : layout == 2 ? (size_t)Smem<256, 2>::TOTAL : (size_t)Smem<256, 0>::TOTAL;
   static_assert(Smem<128, 0>::TOTAL == Smem<128, 1>::TOTAL && Smem<256, 0>::TOTAL == Smem<256, 1>::TOTAL, "layouts share a size");
   // More than RPAD query rows per kv head (large groups, several draft tokens) are served RPAD rows at a time: every
   // pass is a decode launch over the cache plus its combine; the last pass's combine is left to hkv_combine.
@@ -963,7 +1002,7 @@ extern "C" int hkv_decode(const void* q, const void* kd, const void* ksf, const 
                           int qlmax, float sm_scale, float v_scale, const float* gk, const float* gv, void* workspace,
                           size_t workspace_bytes, int splits, void* out, void* stream) {
   return decode_impl(q, kd, ksf, vd, vsf, strides, PS, block_tables, MP, seq_lens, query_start_loc, B, KVH, G, D, qlmax,
-                     sm_scale, v_scale, gk, gv, workspace, workspace_bytes, splits, nullptr, out, stream);
+                     sm_scale, v_scale, gk, gv, workspace, workspace_bytes, splits, nullptr, 0, out, stream);
 }
 
 extern "C" int hkv_decode_rot(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
@@ -974,7 +1013,16 @@ extern "C" int hkv_decode_rot(const void* q, const void* kd, const void* ksf, co
                               void* stream) {
   if (B > 0 && !signs) return HKV_ERR_NULL;
   return decode_impl(q, kd, ksf, vd, vsf, strides, PS, block_tables, MP, seq_lens, query_start_loc, B, KVH, G, D, qlmax,
-                     sm_scale, v_scale, gk, gv, workspace, workspace_bytes, splits, signs, out, stream);
+                     sm_scale, v_scale, gk, gv, workspace, workspace_bytes, splits, signs, 0, out, stream);
+}
+
+extern "C" int hkv_decode_k8(const void* q, const void* kd, const void* vd, const void* vsf, const int64_t strides[6],
+                             int PS, const int32_t* block_tables, int MP, const int32_t* seq_lens,
+                             const int32_t* query_start_loc, int B, int KVH, int G, int D, int qlmax, float sm_scale,
+                             float v_scale, const float* gk, const float* gv, void* workspace, size_t workspace_bytes,
+                             int splits, void* out, void* stream) {
+  return decode_impl(q, kd, kd, vd, vsf, strides, PS, block_tables, MP, seq_lens, query_start_loc, B, KVH, G, D, qlmax,
+                     sm_scale, v_scale, gk, gv, workspace, workspace_bytes, splits, nullptr, 1, out, stream);
 }
 
 extern "C" int hkv_combine(const void* workspace, size_t workspace_bytes, const int32_t* query_start_loc, int B,

@@ -41,7 +41,9 @@ __device__ __forceinline__ uint32_t out_pair(uint32_t h2) {        // f16x2 -> t
   return *reinterpret_cast<const uint32_t*>(&b);
 }
 
-template <int D, int F16>
+// K8 = 1: the K8V4 slot (kv_fp4_ref.py:283-321): a key block is 16 signed E4M3 bytes, converted as they are (the
+// key scale is global); value blocks as above.
+template <int D, int F16, int K8>
 __global__ void __launch_bounds__(256) dequant_kernel(const DequantParams p) {
   constexpr int NB = D / 16;
   pdl_wait();                                     // the cache may come from the preceding launch
@@ -68,6 +70,22 @@ __global__ void __launch_bounds__(256) dequant_kernel(const DequantParams p) {
     btrow = p.bt + (long long)__ldg(p.rows + lo) * p.MP;
   }
   const long long page = __ldg(btrow + pos / p.PS), off = pos % p.PS;
+  uint4* dst = reinterpret_cast<uint4*>((side ? p.out_v : p.out_k) + ((tok * p.KVH + h) * (long long)D + blk * 16) / 2);
+  if (K8 && side == 0) {
+    const uint4 w8 = *reinterpret_cast<const uint4*>(p.kd + page * p.dsp + off * p.dst + h * p.dsh + blk * 16);
+    const uint32_t ws[4] = {w8.x, w8.y, w8.z, w8.w};
+    uint32_t o8[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t lo, hi;
+      e4m3x4_to_f16x2(ws[i], lo, hi);
+      o8[2 * i] = out_pair<F16>(lo);
+      o8[2 * i + 1] = out_pair<F16>(hi);
+    }
+    dst[0] = make_uint4(o8[0], o8[1], o8[2], o8[3]);
+    dst[1] = make_uint4(o8[4], o8[5], o8[6], o8[7]);
+    return;
+  }
   const uint8_t* data = (side ? p.vd : p.kd) + page * p.dsp + off * p.dst + h * p.dsh + blk * 8;
   const uint8_t* scl = (side ? p.vsf : p.ksf) + page * p.ssp + off * p.sst + h * p.ssh + blk;
   const uint2 w = *reinterpret_cast<const uint2*>(data);
@@ -84,18 +102,20 @@ __global__ void __launch_bounds__(256) dequant_kernel(const DequantParams p) {
       e[4 + i] = out_pair<F16>(hmul2h(b[i], s2));
     }
   }
-  uint4* dst = reinterpret_cast<uint4*>((side ? p.out_v : p.out_k) + ((tok * p.KVH + h) * (long long)D + blk * 16) / 2);
   dst[0] = make_uint4(e[0], e[1], e[2], e[3]);
   dst[1] = make_uint4(e[4], e[5], e[6], e[7]);
 }
 
 }  // namespace hkv
 
-extern "C" int hkv_dequant(const void* kd, const void* ksf, const void* vd, const void* vsf, const int64_t strides[6],
-                           int PS, const int32_t* block_tables, int MP, const int32_t* rows, const int32_t* cu,
-                           int n_rows, int64_t start, int64_t n_tokens, void* out_k, void* out_v, int KVH, int D,
-                           int out_f16, void* stream) {
+static int dequant_impl(const void* kd, const void* ksf, const void* vd, const void* vsf, const int64_t strides[6],
+                        int PS, const int32_t* block_tables, int MP, const int32_t* rows, const int32_t* cu, int n_rows,
+                        int64_t start, int64_t n_tokens, void* out_k, void* out_v, int KVH, int D, int out_f16, int k8,
+                        void* stream) {
   using namespace hkv;
+  if (k8 && D != 256) return HKV_ERR_UNSUPPORTED;
+  if (k8 && kd && strides && (((uintptr_t)kd | (uintptr_t)strides[0] | (uintptr_t)strides[1] | (uintptr_t)strides[2]) & 15))
+    return HKV_ERR_ALIGN;
   if (n_tokens < 0 || start < 0 || MP < 0 || n_rows < 0) return HKV_ERR_RANGE;
   if (n_tokens == 0) return HKV_OK;
   if (!kd || !ksf || !vd || !vsf || !strides || !block_tables || !out_k || !out_v) return HKV_ERR_NULL;
@@ -117,7 +137,25 @@ extern "C" int hkv_dequant(const void* kd, const void* ksf, const void* vd, cons
   const long long threads = n_tokens * KVH * (D / 16);
   const long long blocks = (threads + 255) / 256;
   if (blocks > 0x7fffffffll) return HKV_ERR_RANGE;
-  void (*k)(const DequantParams) = D == 128 ? (out_f16 ? dequant_kernel<128, 1> : dequant_kernel<128, 0>)
-                                           : (out_f16 ? dequant_kernel<256, 1> : dequant_kernel<256, 0>);
+  void (*k)(const DequantParams);
+  if (k8) k = out_f16 ? dequant_kernel<256, 1, 1> : dequant_kernel<256, 0, 1>;
+  else if (D == 128) k = out_f16 ? dequant_kernel<128, 1, 0> : dequant_kernel<128, 0, 0>;
+  else k = out_f16 ? dequant_kernel<256, 1, 0> : dequant_kernel<256, 0, 0>;
   return record_cuda(launch_pdl(k, dim3((unsigned)blocks, 2), dim3(256), 0, (cudaStream_t)stream, p));
+}
+
+extern "C" int hkv_dequant(const void* kd, const void* ksf, const void* vd, const void* vsf, const int64_t strides[6],
+                           int PS, const int32_t* block_tables, int MP, const int32_t* rows, const int32_t* cu,
+                           int n_rows, int64_t start, int64_t n_tokens, void* out_k, void* out_v, int KVH, int D,
+                           int out_f16, void* stream) {
+  return dequant_impl(kd, ksf, vd, vsf, strides, PS, block_tables, MP, rows, cu, n_rows, start, n_tokens, out_k, out_v,
+                      KVH, D, out_f16, 0, stream);
+}
+
+extern "C" int hkv_dequant_k8(const void* kd, const void* vd, const void* vsf, const int64_t strides[6], int PS,
+                              const int32_t* block_tables, int MP, const int32_t* rows, const int32_t* cu, int n_rows,
+                              int64_t start, int64_t n_tokens, void* out_k, void* out_v, int KVH, int D, int out_f16,
+                              void* stream) {
+  return dequant_impl(kd, kd, vd, vsf, strides, PS, block_tables, MP, rows, cu, n_rows, start, n_tokens, out_k, out_v,
+                      KVH, D, out_f16, 1, stream);
 }

@@ -166,7 +166,11 @@ __device__ __forceinline__ void score(const float (&ax)[16], float sc, BlockCode
 // reference's butterfly order (kv_fp4_ref.py:31-35, :55-87), and quantised from the fp32 result. The D / 16 lanes of
 // a key row sit side by side in a warp: stages h = 1 .. 8 run inside a lane, the others exchange with the lane
 // 1, 2, 4 (, 8) positions away. Values are never rotated.
-template <int D, int SEARCH, int LPB, int HAD>
+//
+// K8 = 1 (with LPB = 1): the K8V4 slot of the reference (kv_fp4_ref.py:283-311): keys are stored as D signed E4M3
+// bytes, e4m3(k / gk) with an IEEE division, round to nearest even, saturating at +-448 (what vLLM's fp8 cache
+// holds); values keep the FP4 format. A key lane stores 16 bytes instead of 8 code bytes + a scale byte.
+template <int D, int SEARCH, int LPB, int HAD, int K8 = 0>
 __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   constexpr int NB = D / 16;                      // blocks per row
   pdl_wait();                                     // inputs and the cache may come from the preceding launch
@@ -254,6 +258,21 @@ __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
     amax = fmaxf(amax, fmaxf(ax[2 * i], ax[2 * i + 1]));
   }
   const float g = side ? p.gv[h] : p.gk[h];
+  if (K8 && side == 0) {
+    if (!active) return;
+    uint32_t wq[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const unsigned lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(x[4 * i], g), __fdiv_rn(x[4 * i + 1], g)),
+                                                   __NV_SATFINITE, __NV_E4M3);
+      const unsigned hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(x[4 * i + 2], g), __fdiv_rn(x[4 * i + 3], g)),
+                                                   __NV_SATFINITE, __NV_E4M3);
+      wq[i] = lo | (hi << 16);
+    }
+    *reinterpret_cast<uint4*>(p.kd + page * p.dsp + pos * p.dst + h * p.dsh + blk * 16) =
+        make_uint4(wq[0], wq[1], wq[2], wq[3]);
+    return;
+  }
   const int c0 = (int)e4m3_enc(__fdiv_rn(amax, __fmul_rn(g, 6.0f)));
   int cb = c0;
   BlockCodes best;
@@ -352,8 +371,11 @@ int record_cuda(cudaError_t e) {
 static int write_impl(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1, void* kd,
                       void* ksf, void* vd, void* vsf, const int64_t strides[6], int PS, const int64_t* slots,
                       int64_t n_slots, const float* gk, const float* gv, int KVH, int D, int search,
-                      const float* signs, void* stream) {
+                      const float* signs, int k8, void* stream) {
   using namespace hkv;
+  if (k8 && D != 256) return HKV_ERR_UNSUPPORTED;      // the K8V4 slot exists at head_dim 256 only, like the reference's
+  if (k8 && strides && (((uintptr_t)kd | (uintptr_t)strides[0] | (uintptr_t)strides[1] | (uintptr_t)strides[2]) & 15))
+    return HKV_ERR_ALIGN;                              // 16-byte key stores
   if (n_slots < 0) return HKV_ERR_RANGE;
   if (n_slots == 0) return HKV_OK;
   if (!key || !val || !kd || !ksf || !vd || !vsf || !strides || !slots || !gk || !gv) return HKV_ERR_NULL;
@@ -379,14 +401,16 @@ static int write_impl(const void* key, const void* val, int64_t ks0, int64_t ks1
   if (signs && ((uintptr_t)signs & 15)) return HKV_ERR_ALIGN;
   // lanes: one per (token, block) for prefill-sized launches and whenever the keys are rotated, a quad per
   // (token, block) for few tokens (decode appends)
-  const int lpb = (n_slots <= 4096 && !signs) ? 4 : 1;
+  const int lpb = (n_slots <= 4096 && !signs && !k8) ? 4 : 1;
   const int threads = 256;
   const long long lanes = n_slots * (2ll * KVH * (D / 16)) * lpb;
   const long long blocks = (lanes + threads - 1) / threads;
   if (blocks > 0x7fffffffll) return HKV_ERR_RANGE;
   cudaStream_t st = (cudaStream_t)stream;
   void (*k)(const WriteParams);
-  if (signs) {
+  if (k8) {
+    k = search ? write_kernel<256, 1, 1, 0, 1> : write_kernel<256, 0, 1, 0, 1>;
+  } else if (signs) {
     k = D == 128 ? (search ? write_kernel<128, 1, 1, 1> : write_kernel<128, 0, 1, 1>)
                  : (search ? write_kernel<256, 1, 1, 1> : write_kernel<256, 0, 1, 1>);
   } else if (D == 128) {
@@ -404,7 +428,7 @@ extern "C" int hkv_write(const void* key, const void* val, int64_t ks0, int64_t 
                          const int64_t* slots, int64_t n_slots, const float* gk, const float* gv, int KVH, int D,
                          int search, void* stream) {
   return write_impl(key, val, ks0, ks1, vs0, vs1, kd, ksf, vd, vsf, strides, PS, slots, n_slots, gk, gv, KVH, D,
-                    search, nullptr, stream);
+                    search, nullptr, 0, stream);
 }
 
 extern "C" int hkv_write_rot(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1,
@@ -413,5 +437,13 @@ extern "C" int hkv_write_rot(const void* key, const void* val, int64_t ks0, int6
                              int search, const float* signs, void* stream) {
   if (!signs) return HKV_ERR_NULL;
   return write_impl(key, val, ks0, ks1, vs0, vs1, kd, ksf, vd, vsf, strides, PS, slots, n_slots, gk, gv, KVH, D,
-                    search, signs, stream);
+                    search, signs, 0, stream);
+}
+
+extern "C" int hkv_write_k8(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1,
+                            void* kd, void* vd, void* vsf, const int64_t strides[6], int PS, const int64_t* slots,
+                            int64_t n_slots, const float* gk, const float* gv, int KVH, int D, int search,
+                            void* stream) {
+  return write_impl(key, val, ks0, ks1, vs0, vs1, kd, kd, vd, vsf, strides, PS, slots, n_slots, gk, gv, KVH, D, search,
+                    nullptr, 1, stream);
 }

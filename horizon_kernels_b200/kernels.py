@@ -94,8 +94,8 @@ def write(key, value, flat, strides, PS, slot_mapping, gk, gv, search=True, sign
     signs (D,) fp32 of +-1 on the device: the keys are rotated (FWHT(k * signs) * D^-0.5 in fp32) before they are
     quantised. Bit-exact to the reference's write_reference (kv_fp4_ref.py:233-245). Signature of
     kv_fp4_serving.py:994."""
-    if k8:
-        raise NotImplementedError("the K8V4 slot is not built")
+    if k8 and signs is not None:
+        raise ValueError("the K8V4 slot keeps FP8 keys: no rotation")
     _need_cuda(key, value, slot_mapping, gk, gv, *flat)
     _check_signs(signs, key.shape[2])
     if key.dtype != torch.bfloat16 or value.dtype != torch.bfloat16:
@@ -113,7 +113,9 @@ def write(key, value, flat, strides, PS, slot_mapping, gk, gv, search=True, sign
             _ptr(vd), _ptr(vsf), st, int(PS), _ptr(slot_mapping), slot_mapping.shape[0], _ptr(gk), _ptr(gv), KVH, D,
             int(bool(search)))
     with torch.cuda.device(key.device):
-        if signs is None:
+        if k8:                  # flat = (key bytes, unused, value codes, value scales)
+            rc = _lib.load().hkv_write_k8(*args[:6], _ptr(kd), _ptr(vd), _ptr(vsf), *args[10:], _stream())
+        elif signs is None:
             rc = _lib.load().hkv_write(*args, _stream())
         else:
             rc = _lib.load().hkv_write_rot(*args, _ptr(signs), _stream())
@@ -130,8 +132,8 @@ def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_
     (nst, ncw, min_chunk, tw) are accepted and ignored. signs (D,) fp32 of +-1 on the device: the keys in the cache
     were written rotated, and the kernel rotates the UNROTATED query it is given the same way.
     Signature of kv_fp4_serving.py:894-895."""
-    if k8:
-        raise NotImplementedError("the K8V4 slot is not built")
+    if k8 and signs is not None:
+        raise ValueError("the K8V4 slot keeps FP8 keys: no rotation")
     _need_cuda(query, block_tables, seq_lens, query_start_loc, gk, gv, out, workspace, *flat)
     _check_signs(signs, query.shape[2])
     if query.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -155,7 +157,12 @@ def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_
         args = (_ptr(query), _ptr(kd), _ptr(ksf), _ptr(vd), _ptr(vsf), st, int(PS), _ptr(block_tables), MP,
                 _ptr(seq_lens), _ptr(query_start_loc), B, KVH, G, D, int(qlmax), float(bmm1_scale), float(bmm2_scale),
                 _ptr(gk), _ptr(gv), _ptr(workspace), wsb, S)
-        rc = L.hkv_decode(*args, _ptr(out), s) if signs is None else L.hkv_decode_rot(*args, _ptr(signs), _ptr(out), s)
+        if k8:
+            rc = L.hkv_decode_k8(args[0], args[1], *args[3:], _ptr(out), s)
+        elif signs is None:
+            rc = L.hkv_decode(*args, _ptr(out), s)
+        else:
+            rc = L.hkv_decode_rot(*args, _ptr(signs), _ptr(out), s)
         _lib.check(rc, "hkv_decode")
         if not _combine:                      # (benchmark only: time the decode kernel alone; `out` is incomplete)
             return out
@@ -166,8 +173,6 @@ def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_
 
 
 def _dequant(flat, strides, PS, block_tables, MP, rows, cu, n_rows, start, n_tokens, out_k, out_v, k8):
-    if k8:
-        raise NotImplementedError("the K8V4 slot is not built")
     _need_cuda(block_tables, out_k, out_v, *flat)
     if out_k.dtype not in (torch.bfloat16, torch.float16) or out_v.dtype != out_k.dtype:
         raise TypeError("out_k / out_v must both be bf16 or both fp16")
@@ -180,11 +185,14 @@ def _dequant(flat, strides, PS, block_tables, MP, rows, cu, n_rows, start, n_tok
     KVH, D = out_k.shape[1], out_k.shape[2]
     kd, ksf, vd, vsf = flat
     st = (C.c_int64 * 6)(*strides)
+    tail = (st, int(PS), _ptr(block_tables), int(MP), None if rows is None else _ptr(rows),
+            None if cu is None else _ptr(cu), int(n_rows), int(start), int(n_tokens), _ptr(out_k), _ptr(out_v), KVH, D,
+            int(out_k.dtype == torch.float16))
     with torch.cuda.device(out_k.device):
-        rc = _lib.load().hkv_dequant(_ptr(kd), _ptr(ksf), _ptr(vd), _ptr(vsf), st, int(PS), _ptr(block_tables), int(MP),
-                                     None if rows is None else _ptr(rows), None if cu is None else _ptr(cu), int(n_rows),
-                                     int(start), int(n_tokens), _ptr(out_k), _ptr(out_v), KVH, D,
-                                     int(out_k.dtype == torch.float16), _stream())
+        if k8:
+            rc = _lib.load().hkv_dequant_k8(_ptr(kd), _ptr(vd), _ptr(vsf), *tail, _stream())
+        else:
+            rc = _lib.load().hkv_dequant(_ptr(kd), _ptr(ksf), _ptr(vd), _ptr(vsf), *tail, _stream())
     _lib.check(rc, "hkv_dequant")
 
 

@@ -70,3 +70,26 @@ def flat_views(k_data, k_sf, v_data, v_sf):
         raise ValueError("K and V views must share their strides")
     st = tuple(int(x) for x in (*k_data.stride()[:3], *k_sf.stride()[:3]))
     return (flat(k_data), flat(k_sf), flat(v_data), flat(v_sf)), st
+
+
+K8_SLOT = 400                    # K8V4 slot at head_dim 256: [256 e4m3 key bytes | 128 value codes | 16 value scales]
+
+
+def k8_slot_bytes(D: int) -> int:
+    return D + D // 2 + D // 16
+
+
+def k8_views(kv_cache: torch.Tensor, D: int = 256):
+    """K8V4 cache, logical (pages, KVH, PS, slot) uint8 -> (kd, vd, vsf) as [page, position, head, byte] views: key
+    bytes, value codes, value scales (reference `split_views_k8`, kv_fp4_ref.py:290-293)"""
+    if kv_cache.dtype != torch.uint8 or kv_cache.dim() != 4 or kv_cache.shape[3] != k8_slot_bytes(D):
+        raise ValueError(f"K8V4 cache must be uint8 (pages, KVH, PS, {k8_slot_bytes(D)})")
+    t = kv_cache.permute(0, 2, 1, 3)
+    return t[..., :D], t[..., D:D + D // 2], t[..., D + D // 2:]
+
+
+def k8_flat_views(kd, vd, vsf):
+    """(kd, vd, vsf) views -> the four-entry `flat` tuple and six strides the kernel wrappers take; the key-scale entry
+    is a placeholder (the value scales again), as in the reference's backend (backend.py:287-291)"""
+    (fk, fs, fv, fvs), st = flat_views(kd, vsf, vd, vsf)
+    return (fk, fvs, fv, fvs), st

@@ -164,6 +164,28 @@ int hkv_dequant(const void* kd, const void* ksf, const void* vd, const void* vsf
                 int64_t n_tokens, void* out_k, void* out_v, int KVH, int D, int out_f16, void* stream);
 
 /*
+ * The three operations on the reference's K8V4 slot (kv_fp4_ref.py:283-321; `HORIZON_KVFP4_K8`), head_dim 256 only:
+ * per (token, kv head) 400 bytes = [256 signed E4M3 key bytes | 128 value code bytes | 16 value scale bytes], cache
+ * (pages, KVH, PS, 400) with heads outermost. kd / vd / vsf point at the key bytes, value codes and value scales of
+ * (page 0, position 0, head 0); strides = {page, position, head} byte strides of kd and vd, then of vsf.
+ *   hkv_write_k8   keys e4m3(k / gk[h]) (IEEE division, round to nearest even, saturating at +-448, what vLLM's fp8 cache
+ *                  holds), values like hkv_write: byte-exact to `write_reference_k8` (kv_fp4_ref.py:301-311)
+ *   hkv_decode_k8  like hkv_decode with key = e4m3 value * gk[h]; followed by hkv_combine. The slots of a head's 16
+ *                  tokens must be contiguous (dst == 400)
+ *   hkv_dequant_k8 like hkv_dequant; keys are the E4M3 values themselves (no gk)
+ */
+int hkv_write_k8(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1, void* kd, void* vd,
+                 void* vsf, const int64_t strides[6], int PS, const int64_t* slots, int64_t n_slots, const float* gk,
+                 const float* gv, int KVH, int D, int search, void* stream);
+int hkv_decode_k8(const void* q, const void* kd, const void* vd, const void* vsf, const int64_t strides[6], int PS,
+                  const int32_t* block_tables, int MP, const int32_t* seq_lens, const int32_t* query_start_loc, int B,
+                  int KVH, int G, int D, int qlmax, float sm_scale, float v_scale, const float* gk, const float* gv,
+                  void* workspace, size_t workspace_bytes, int splits, void* out, void* stream);
+int hkv_dequant_k8(const void* kd, const void* vd, const void* vsf, const int64_t strides[6], int PS,
+                   const int32_t* block_tables, int MP, const int32_t* rows, const int32_t* cu, int n_rows, int64_t start,
+                   int64_t n_tokens, void* out_k, void* out_v, int KVH, int D, int out_f16, void* stream);
+
+/*
  * Process-wide options. No counterpart in the reference.
  *   HKV_OPT_EARLY_METADATA (0 = off, the default; 1 = on): the caller states that `seq_lens` and `query_start_loc` of
  *     every later hkv_decode / hkv_decode_noalloc call are complete before the kernel that PRECEDES the call on its
