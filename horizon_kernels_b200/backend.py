@@ -23,7 +23,7 @@ from typing import ClassVar
 import torch
 
 from . import kernels as K
-from .layout import flat_views, slot_bytes, slot_views
+from .layout import flat_views, k8_flat_views, k8_slot_bytes, k8_views, slot_bytes, slot_views
 
 HEAD_SIZES = (128, 256)
 PAGE_SIZES = (16, 32, 64)
@@ -91,6 +91,10 @@ def _build_classes():
                 return spec
             if spec.head_size not in HEAD_SIZES or spec.head_size_v != spec.head_size:
                 raise ValueError(f"horizon_kvfp4 needs head_dim in {HEAD_SIZES}, got {spec.head_size}")
+            if _env("HORIZON_KVFP4_K8", "0") == "1":          # FP8 keys + FP4 values: one 400-byte slot per kv head
+                if spec.head_size != 256:
+                    raise ValueError("the K8V4 slot (HORIZON_KVFP4_K8) exists at head_dim 256 only")
+                return replace(spec, num_head_slots=spec.num_kv_heads, state_content_bytes=k8_slot_bytes(256))
             return replace(spec, num_head_slots=2 * spec.num_kv_heads, state_content_bytes=slot_bytes(spec.head_size))
 
         @staticmethod
@@ -208,8 +212,10 @@ def _build_classes():
             self.kv_sharing_target_layer_name = None
             self.sliding_window = None
             self.G = self.num_heads // self.num_kv_heads
-            if _env("HORIZON_KVFP4_K8", "0") == "1":
-                raise NotImplementedError("the K8V4 slot (HORIZON_KVFP4_K8) is not built")
+            # HORIZON_KVFP4_K8=1: the K8V4 slot (FP8 keys, FP4 values; reference backend.py:50-54, :211-212)
+            self.k8 = _env("HORIZON_KVFP4_K8", "0") == "1"
+            if self.k8 and (head_size != 256 or _env("HORIZON_KVFP4_HAD", "0") == "1"):
+                raise ValueError("HORIZON_KVFP4_K8 needs head_dim 256 and keeps FP8 keys: the rotation must be off")
             # HORIZON_KVFP4_HAD=1: keys are written rotated (Hadamard) and queries rotated inside the decode kernel
             # (reference backend.py:214-222, kv_fp4_ref.py:31-35)
             self.had = _env("HORIZON_KVFP4_HAD", "0") == "1"
@@ -256,8 +262,13 @@ def _build_classes():
             v = self._views
             if v is not None and v[0] == kv_cache.data_ptr() and v[1] == tuple(kv_cache.stride()):
                 return v[2]
-            views = slot_views(kv_cache, self.num_kv_heads, self.head_size)
-            flat, strides = flat_views(*views)
+            if self.k8:                                           # (blocks, KVH, PS, 400)
+                if kv_cache.shape[1] != self.num_kv_heads:
+                    raise ValueError(f"K8V4 cache must have one slot per kv head, got shape {tuple(kv_cache.shape)}")
+                flat, strides = k8_flat_views(*k8_views(kv_cache, self.head_size))
+            else:
+                views = slot_views(kv_cache, self.num_kv_heads, self.head_size)
+                flat, strides = flat_views(*views)
             out = dict(flat=flat, strides=strides, PS=kv_cache.shape[2])
             self._views = (kv_cache.data_ptr(), tuple(kv_cache.stride()), out)
             return out
@@ -290,7 +301,7 @@ def _build_classes():
             k3 = key.view(key.shape[0], self.num_kv_heads, D) if key.dim() == 2 else key
             v3 = value.view(value.shape[0], self.num_kv_heads, D) if value.dim() == 2 else value
             K.write(k3, v3, v["flat"], v["strides"], v["PS"], slot_mapping, gk, gv, self.search,
-                    signs=self._rot(key.device))
+                    signs=self._rot(key.device), k8=self.k8)
 
         # -------------------------------------------------------------------------------------------- forward
         def forward(self, layer, query, key, value, kv_cache, attn_metadata, output, output_scale=None,
@@ -314,7 +325,7 @@ def _build_classes():
             if m.has_decode and m.num_reqs > 0:
                 K.decode_ragged(q, v["flat"], v["strides"], v["PS"], m.block_table, m.seq_lens, m.query_start_loc,
                                 self.scale, float(layer._v_scale_float), gk, gv, m.qlmax, out, st["ws"],
-                                splits=self.cps or None, signs=self._rot(q.device))
+                                splits=self.cps or None, signs=self._rot(q.device), k8=self.k8)
             if m.prefill_rows:
                 self._prefill_rows(layer, q, v, m, out)
             return output
@@ -334,7 +345,8 @@ def _build_classes():
                     continue
                 kk = torch.empty((L, KVH, D), dtype=torch.bfloat16, device=q.device)
                 vv = torch.empty_like(kk)
-                K.dequant_tokens(v["flat"], v["strides"], v["PS"], m.block_table[row].contiguous(), 0, L, kk, vv)
+                K.dequant_tokens(v["flat"], v["strides"], v["PS"], m.block_table[row].contiguous(), 0, L, kk, vv,
+                                 k8=self.k8)
                 qi = q[q0:q1]
                 if self.had:                                                     # the cached keys are rotated
                     qi = K.rotate(qi, self._rot(q.device)).to(torch.bfloat16)

@@ -23,8 +23,9 @@ def test_backend_capabilities():
     assert B.get_impl_cls() is BE.HorizonFp4Impl and B.get_builder_cls() is BE.HorizonFp4Builder
 
 
-def test_customize_spec_sets_two_slots_per_kv_head():
+def test_customize_spec_sets_two_slots_per_kv_head(monkeypatch):
     from dataclasses import dataclass
+    monkeypatch.delenv("HORIZON_KVFP4_K8", raising=False)
 
     @dataclass
     class Spec:
@@ -42,6 +43,13 @@ def test_customize_spec_sets_two_slots_per_kv_head():
     assert BE.HorizonFp4Backend.customize_spec(untouched) is untouched
     with pytest.raises(ValueError):
         BE.HorizonFp4Backend.customize_spec(Spec(64, 64, 8, SimpleNamespace(is_nvfp4=True)))
+    monkeypatch.setenv("HORIZON_KVFP4_K8", "1")                       # K8V4: one 400-byte slot per kv head
+    s = BE.HorizonFp4Backend.customize_spec(Spec(256, 256, 2, SimpleNamespace(is_nvfp4=True)))
+    assert s.num_head_slots == 2 and s.state_content_bytes == 400
+    with pytest.raises(ValueError):
+        BE.HorizonFp4Backend.customize_spec(Spec(128, 128, 8, SimpleNamespace(is_nvfp4=True)))
+    with pytest.raises(ValueError):
+        BE.HorizonFp4Impl(32, 128, 0.1, num_kv_heads=8, kv_cache_dtype="nvfp4")
 
 
 def test_impl_constructor_checks():

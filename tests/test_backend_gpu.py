@@ -141,3 +141,39 @@ def test_rotation_option_end_to_end(monkeypatch):
     from cases import errors
     mx, mn, rl = errors(output.view(NT, HQ, D), ref)
     assert rl <= 2.5e-3 and mn <= 2e-3 and mx <= 6e-2, (mx, mn, rl)
+
+
+def test_k8v4_option_end_to_end(monkeypatch):
+    """HORIZON_KVFP4_K8=1: a (blocks, KVH, PS, 400) cache, FP8 keys and FP4 values through do_kv_cache_update + forward
+    (decode rows and a prefill row) against the oracle"""
+    monkeypatch.setenv("HORIZON_KVFP4_K8", "1")
+    KVH, G, D, PS = 2, 8, 256, 16
+    lens, qls = [500, 90, 64], [1, 30, 1]
+    c = synth.paged_case(99, lens, KVH, G, D, PS, outliers=True, ql_list=qls)
+    dev = torch.device("cuda")
+    B, HQ, NT = len(lens), KVH * G, sum(qls)
+    kscale, vscale = 0.25, 1.0
+    layer = SimpleNamespace(_k_scale_float=kscale, _v_scale_float=vscale, layer_name="model.layers.2.self_attn.attn")
+    impl = BE.HorizonFp4Impl(HQ, D, D ** -0.5, num_kv_heads=KVH, kv_cache_dtype="nvfp4", max_num_seqs=8)
+    assert impl.k8
+    kv_cache = torch.full((c["NP"], KVH, PS, 400), 0x7F, dtype=torch.uint8, device=dev)
+    impl.do_kv_cache_update(layer, bf16_tensor(c["key"]), bf16_tensor(c["val"]), kv_cache,
+                            torch.from_numpy(c["slots"]).to(dev))
+    lay = O.Layout.k8_slots(PS, KVH, D)
+    gk, gv = np.full(KVH, kscale, np.float32), np.full(KVH, vscale, np.float32)
+    want = np.full(kv_cache.numel(), 0x7F, np.uint8)
+    O.write(c["key"], c["val"], want, lay, c["slots"], gk, gv, True)
+    assert np.array_equal(kv_cache.cpu().numpy().reshape(-1), want)
+    qsl = torch.from_numpy(c["qsl"])
+    cam = SimpleNamespace(num_reqs=B, num_actual_tokens=NT, query_start_loc=qsl.to(dev), query_start_loc_cpu=qsl,
+                          seq_lens=torch.from_numpy(c["seq_lens"]).to(dev),
+                          block_table_tensor=torch.from_numpy(c["bt"]).to(dev),
+                          slot_mapping=torch.zeros(NT, dtype=torch.int64, device=dev),
+                          seq_lens_cpu_upper_bound=torch.from_numpy(c["seq_lens"]))
+    meta = BE.HorizonFp4Builder().build(0, cam)
+    output = torch.zeros((NT, HQ * D), dtype=torch.bfloat16, device=dev)
+    impl.forward(layer, bf16_tensor(c["q"]).view(NT, HQ * D), None, None, kv_cache, meta, output)
+    ref, _ = O.attention(c["q"], want, lay, c["bt"], c["seq_lens"], c["qsl"], KVH, D ** -0.5, gk, gv, 1.0)
+    from cases import errors
+    mx, mn, rl = errors(output.view(NT, HQ, D), ref)
+    assert rl <= 2.5e-3 and mn <= 2e-3 and mx <= 6e-2, (mx, mn, rl)
