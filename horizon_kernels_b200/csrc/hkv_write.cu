@@ -347,7 +347,7 @@ extern "C" const char* hkv_error_string(int code) {
     case HKV_OK: return "ok";
     case HKV_ERR_NULL: return "a required pointer is null";
     case HKV_ERR_ALIGN: return "a pointer or stride misses the required alignment";
-    case HKV_ERR_UNSUPPORTED: return "unsupported head_dim, group size, page size, query length or layout";
+    case HKV_ERR_UNSUPPORTED: return "unsupported head_dim, group size, page size or layout";
     case HKV_ERR_SPLITS: return "more than 64 splits";
     case HKV_ERR_WORKSPACE: return "workspace too small";
     case HKV_ERR_RANGE: return "a size is negative or too large";

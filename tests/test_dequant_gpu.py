@@ -93,5 +93,6 @@ def test_dequant_misuse_raises():
         K.dequant_tokens(cache.flat, cache.strides, 16, bt[0].contiguous(), 0, 40, ok, ok.half())
     with pytest.raises(ValueError):
         K.dequant_tokens(cache.flat, cache.strides, 16, bt[0].contiguous(), 0, 41, ok, torch.empty_like(ok))
-    with pytest.raises(NotImplementedError):
+    from horizon_kernels_b200 import _lib
+    with pytest.raises(_lib.HkvError, match="unsupported"):          # the K8V4 slot exists at head_dim 256 only
         K.dequant_tokens(cache.flat, cache.strides, 16, bt[0].contiguous(), 0, 40, ok, torch.empty_like(ok), k8=True)
