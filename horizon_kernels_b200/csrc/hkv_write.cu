@@ -112,11 +112,15 @@ __device__ __forceinline__ BlockCodes block_codes_fast(const float (&ax)[16], fl
   }
   if (diff[0] | diff[1]) {                        // rare: some quotient lies within 2^-20 of a rounding boundary
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int sh = 4 * (i & 7);
-      if ((diff[i >> 3] >> sh) & 15u) {
-        const unsigned k = resolve_code(ax[i], s, (c.w[i >> 3] >> sh) & 7u);
-        c.w[i >> 3] = (c.w[i >> 3] & ~(15u << sh)) | (k << sh);
+    for (int q4 = 0; q4 < 4; ++q4) {                // four values at a time: most groups have no such quotient
+      if (((diff[q4 >> 1] >> (16 * (q4 & 1))) & 0xffffu) == 0u) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = 4 * q4 + j, sh = 4 * (i & 7);
+        if ((diff[i >> 3] >> sh) & 15u) {
+          const unsigned k = resolve_code(ax[i], s, (c.w[i >> 3] >> sh) & 7u);
+          c.w[i >> 3] = (c.w[i >> 3] & ~(15u << sh)) | (k << sh);
+        }
       }
     }
   }
