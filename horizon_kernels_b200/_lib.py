@@ -8,7 +8,8 @@ LIB_PATH = os.path.join(HERE, "lib", "libhkv.so")
 
 EXPORTS = ("hkv_version", "hkv_error_string", "hkv_last_cuda_error", "hkv_write", "hkv_decode_workspace_bytes",
            "hkv_decode", "hkv_combine", "hkv_workspace_status", "hkv_decode_noalloc", "hkv_set_option", "hkv_dequant", "hkv_write_rot",
-           "hkv_decode_rot", "hkv_write_k8", "hkv_decode_k8", "hkv_dequant_k8")
+           "hkv_decode_rot", "hkv_write_k8", "hkv_decode_k8", "hkv_dequant_k8",
+           "hkv_selftest_wait_timeout")
 
 _lib = None
 
@@ -64,6 +65,8 @@ def load():
         L.hkv_dequant_k8.restype = i32
         L.hkv_dequant_k8.argtypes = [vp, vp, vp, C.POINTER(i64), i32, vp, i32, vp, vp, i32, i64, i64, vp, vp, i32, i32,
                                      i32, vp]
+        L.hkv_selftest_wait_timeout.restype = i32
+        L.hkv_selftest_wait_timeout.argtypes = [vp, i64, vp]
         L.hkv_set_option.restype = i32
         L.hkv_set_option.argtypes = [i32, i32]
         L.hkv_workspace_status.restype = i32

@@ -100,11 +100,11 @@ __device__ __forceinline__ bool mbar_try_wait_u32(uint32_t bar, uint32_t parity)
       : "memory");
   return ok != 0;
 }
-static __device__ __noinline__ bool mbar_wait_bounded_u32(uint32_t bar, uint32_t parity) {
+static __device__ __noinline__ bool mbar_wait_bounded_u32(uint32_t bar, uint32_t parity, long long limit = kWaitCycles) {
   if (mbar_try_wait_u32(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait_u32(bar, parity)) {
-    if (clock64() - t0 > kWaitCycles) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }

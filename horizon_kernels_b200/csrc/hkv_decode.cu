@@ -1058,6 +1058,28 @@ extern "C" int hkv_set_option(int option, int value) {
   return HKV_OK;
 }
 
+namespace hkv {
+// One warp waits, with the decode kernel's bounded wait but a caller-given limit, on a barrier that nothing completes,
+// and reports the way the decode kernel does. It never hangs: the wait gives up after `cycles` SM clocks.
+__global__ void selftest_wait_kernel(uint8_t* ws, long long cycles) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) mbar_init(&bar, 1);
+  fence_barrier_init();
+  __syncthreads();
+  if (!mbar_wait_bounded_u32(smem_u32(&bar), 0, cycles)) {
+    if (threadIdx.x == 0) atomicExch(&reinterpret_cast<Header*>(ws)->status, HKV_ERR_DEVICE_WAIT);
+  }
+}
+}  // namespace hkv
+
+extern "C" int hkv_selftest_wait_timeout(void* workspace, int64_t cycles, void* stream) {
+  using namespace hkv;
+  if (!workspace) return HKV_ERR_NULL;
+  if (cycles < 0 || cycles > (1ll << 31)) return HKV_ERR_RANGE;     // at most about a second
+  selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((uint8_t*)workspace, cycles);
+  return record_cuda(cudaGetLastError());
+}
+
 extern "C" int hkv_workspace_status(void* workspace, int* status, void* stream) {
   using namespace hkv;
   if (!workspace || !status) return HKV_ERR_NULL;

@@ -199,6 +199,14 @@ int hkv_dequant_k8(const void* kd, const void* vd, const void* vsf, const int64_
 int hkv_set_option(int option, int value);
 
 /*
+ * Self-test of the failure path, no counterpart in the reference: one warp waits on a barrier that nothing will ever
+ * complete, with the decode kernel's bounded wait and a limit of `cycles` SM clocks (at most 2^31, about a second), gives
+ * up and records HKV_ERR_DEVICE_WAIT in the workspace header, where hkv_workspace_status finds it. The kernel always
+ * terminates and the context stays usable; nothing faults.
+ */
+int hkv_selftest_wait_timeout(void* workspace, int64_t cycles, void* stream);
+
+/*
  * Copies the workspace's device status word to *status (HKV_OK or HKV_ERR_DEVICE_WAIT) and clears it. Synchronises the
  * stream: a debugging aid, not for the hot path.
  */

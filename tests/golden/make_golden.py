@@ -146,7 +146,7 @@ def attention_cases(R):
 
 
 def config0(R):
-    """BASELINE config 0: batch 4, 32 q heads / 8 kv heads, head_dim 128, 2048 cached tokens each, page 16, page table
+    """benchmark configuration 0: batch 4, 32 q heads / 8 kv heads, head_dim 128, 2048 cached tokens each, page 16, page table
     a permutation of 512 pages, q / k / v ~ N(0,1) bf16, scale 1/sqrt(128), per-tensor global scale amax/(6*448)."""
     B, KVH, G, D, PS, L = 4, 8, 4, 128, 16, 2048
     c = synth.paged_case(900, [L] * B, KVH, G, D, PS, extra_pages=1)   # its page table is replaced below

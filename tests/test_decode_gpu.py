@@ -250,6 +250,24 @@ def test_length_beyond_the_block_table_is_cut_at_its_reach():
     assert torch.equal(got, want)
 
 
+def test_bounded_wait_reports_instead_of_hanging():
+    """the failure path of every device-side wait: a wait on a barrier that nothing completes gives up after its limit
+    (here 2 million cycles, about a millisecond), records HKV_ERR_DEVICE_WAIT in the workspace header, the kernel ends,
+    and the same workspace then serves a normal decode"""
+    import ctypes as C
+    c = build_decode_case(2470, [100], 2, 4, 128, 16)
+    ws = K.alloc_workspace(1, 2, 4, 128, 1, "cuda")
+    L = _lib.load()
+    rc = L.hkv_selftest_wait_timeout(C.c_void_p(ws.data_ptr()), 2_000_000,
+                                     C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    assert K.workspace_status(ws) == -8                          # HKV_ERR_DEVICE_WAIT, cleared by the read
+    assert K.workspace_status(ws) == 0
+    out, _ = gpu_decode(c, ws=ws)
+    assert K.workspace_status(ws) == 0
+    assert_close(out, oracle_decode(c))
+
+
 def test_unsupported_shapes_raise():
     with pytest.raises(_lib.HkvError):
         K.alloc_workspace(1, 1, 65, 128, 1)                                # more than 64 query rows per kv head

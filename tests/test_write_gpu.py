@@ -126,7 +126,7 @@ def test_write_graph_replay():
 
 @pytest.mark.parametrize("search", [True, False])
 def test_config3_fill_then_appends(search):
-    """BASELINE config 3 at full size: a prefill write of 32768 tokens x 8 kv heads x 128 into random pages, then 256
+    """benchmark configuration 3 at full size: a prefill write of 32768 tokens x 8 kv heads x 128 into random pages, then 256
     steps appending one token to each of 128 sequences (crossing page boundaries); every cache byte, canaries of the
     untouched pages included, equal to the oracle's, with the scale search on and off"""
     KVH, D, PS = 8, 128, 16
