@@ -124,11 +124,15 @@ def build_batches(cfg, seed, device, n_batches=2, rows=None, lens_seed=None):
     flat, strides = Lt.flat_views(*Lt.slot_views(pool, KVH, D))
     batches, used = [], 0
     for bi in range(n_batches):
-        lens = draw_lens(cfg, (seed if lens_seed is None else lens_seed) * 131 + bi)
-        if rows is not None:
-            lens = [lens[r] for r in rows]
-        pages = [(L + PS - 1) // PS for L in lens]
-        tot = sum(pages)
+        # (a rank whose draw does not fit what is left of the pool draws again: the pool size is the configuration's)
+        for attempt in range(256):
+            lens = draw_lens(cfg, (seed if lens_seed is None else lens_seed) * 131 + bi + 7919 * attempt)
+            if rows is not None:
+                lens = [lens[r] for r in rows]
+            pages = [(L + PS - 1) // PS for L in lens]
+            tot = sum(pages)
+            if used + tot <= n_pool or lens_seed is not None:
+                break
         if used + tot > n_pool:
             raise RuntimeError("page pool too small for the batches")
         mine = perm[used:used + tot]
@@ -289,7 +293,8 @@ def main():
         pool, (flat, strides), gk, gv, batches = build_batches(cfg, args.seed + 1000 * rank, device, NBT, rows, args.seed)
         B = len(rows)
     else:
-        pool, (flat, strides), gk, gv, batches = build_batches(cfg, args.seed + 1000 * rank, device, NBT)
+        # weak scaling: every rank gets the same context lengths (the same work) on its own pages and data
+        pool, (flat, strides), gk, gv, batches = build_batches(cfg, args.seed + 1000 * rank, device, NBT, None, args.seed)
     for bt in batches:
         bt.qsl_cpu = bt.qsl.cpu()
     impl = BE.HorizonFp4Impl(HQ, D, float(D) ** -0.5, num_kv_heads=KVH, kv_cache_dtype="nvfp4", max_num_seqs=max(B, 1))
