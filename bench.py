@@ -260,6 +260,7 @@ def main():
     ap.add_argument("--ref-tokens", type=int, default=150000, help="cached tokens per step of the CPU arm's sample")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the cpu_baseline leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline / parity leg")
+    ap.add_argument("--shard", default=None, help="R/N: on one GPU, run only shard R of N of a sharded workload (c4)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -289,7 +290,8 @@ def main():
         # one batch for the whole job, partitioned by cached tokens; every rank builds only its own requests
         from horizon_kernels_b200.sharding import partition_requests
         lens_all = draw_lens(cfg, args.seed * 131)
-        rows = partition_requests(lens_all, world)[rank]
+        shard_r, shard_n = (int(x) for x in args.shard.split("/")) if (args.shard and world == 1) else (rank, world)
+        rows = partition_requests(lens_all, shard_n)[shard_r]
         pool, (flat, strides), gk, gv, batches = build_batches(cfg, args.seed + 1000 * rank, device, NBT, rows, args.seed)
         B = len(rows)
     else:
@@ -455,7 +457,7 @@ def main():
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms, dec_ms_avg = (float(x) for x in times.cpu())
     ms_step = ms_total / args.steps
-    n_req = cfg["B"] if cfg.get("sharded") else B * world        # requests of the whole job per step
+    n_req = (B if args.shard else cfg["B"]) if cfg.get("sharded") else B * world   # requests of the whole job per step
     value = n_req / (ms_step * 1e-3)
     e2e_value = n_req / (e2e_ms / args.steps * 1e-3)
 

@@ -29,6 +29,15 @@
 
 #include "hkv_common.cuh"
 
+// tuning constants (they can be overridden on the command line of the compiler for experiments)
+#ifndef HKV_PC128
+#define HKV_PC128 8
+#define HKV_PC256 12
+#endif
+#ifndef HKV_QPREFETCH
+#define HKV_QPREFETCH 1
+#endif
+
 namespace hkv {
 
 #ifndef HKV_TG
@@ -95,6 +104,10 @@ struct Geo {
   static constexpr int V_BASE = K8 ? D : TILE;         // first value byte of the stage (of row 0)
   static constexpr int SF_BASE = LAYOUT == 1 ? UT * SD : SD;        // value / key scales behind their side's codes
   static constexpr int SF_ROW = K8 ? SLOT8 : LAYOUT == 0 ? SLOT : SS;
+  // What a sequence costs a partition beyond its units (locating it, loading its queries, the end-of-piece merge and
+  // the output), in units: measured 3 to 4 microseconds per piece. The stream that is cut into equal partitions counts
+  // every sequence as PIECE_COST + its units, so partitions that hold many short sequences get fewer units.
+  static constexpr int PIECE_COST = D == 128 ? HKV_PC128 : HKV_PC256;
   static constexpr int KS = D / 16;                    // k-steps of K Q^T == mma tiles of V^T P^T (per 16 tokens)
   static constexpr int NBL = D / 64;                   // 16-channel blocks of one key row held by one lane
   static constexpr int NH = D / 128;                   // 16-channel blocks of one value row held by one lane
@@ -171,11 +184,13 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   const bool early = p.early_meta != 0;
   if (!early) pdl_wait();
 
-  // ---- coarse prefix of units per request: coarse[k] = sum of U_b over b < 32 k
+  // ---- coarse prefix of the weight (units + piece cost) per request and head: coarse[k] = sum over b < 32 k
+  constexpr int PC = Gm::PIECE_COST;
+  auto wt = [](int U) { return U > 0 ? U + PC : 0; };
   const int ngrp = (B + 31) >> 5;
   for (int grp = w; grp < ngrp; grp += TG) {
     const int b = grp * 32 + lane;
-    int u = b < B ? load_req<LOG_UT>(p, b).U : 0;
+    int u = b < B ? wt(load_req<LOG_UT>(p, b).U) : 0;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) u += __shfl_xor_sync(0xffffffffu, u, o);
     if (lane == 0) coarse[grp + 1] = u;
@@ -225,10 +240,9 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
     }
     return;
   }
-  const int n_units = (int)(hi - lo);
 
   // ---- locate the request that holds stream position lo (warp-uniform, every warp for itself)
-  int b0, base0;                                   // request and units of earlier requests (per head)
+  int b0, base0;                                   // request and weight of earlier requests (per head)
   {
     int lo_g = 0, hi_g = ngrp;                     // largest grp with coarse[grp] * KVH <= lo
     while (hi_g - lo_g > 1) {
@@ -236,7 +250,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       if ((long long)coarse[mid] * KVH <= lo) lo_g = mid; else hi_g = mid;
     }
     const int b = lo_g * 32 + lane;
-    const int u = b < B ? load_req<LOG_UT>(p, b).U : 0;
+    const int u = b < B ? wt(load_req<LOG_UT>(p, b).U) : 0;
     int incl = u;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -249,15 +263,39 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
     base0 = coarse[lo_g] + __shfl_sync(0xffffffffu, incl - u, j);
   }
 
+  // ---- units (not cost slots) of the partition: request b with weighted start S holds, before stream position x,
+  // floor(t / W) * U + max(0, t mod W - PC) units, t = min(x - S, KVH * W); 32 requests at a time
+  int n_units = 0;
+  for (int grp = b0 >> 5; grp < ngrp && (long long)coarse[grp] * KVH < hi; ++grp) {
+    const int b = grp * 32 + lane;
+    const int U = b < B ? load_req<LOG_UT>(p, b).U : 0, W = wt(U);
+    int incl = W;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    const long long S = (long long)(coarse[grp] + incl - W) * KVH;
+    auto before = [&](long long x) -> long long {
+      if (W == 0 || x <= S) return 0;
+      const long long t = min(x - S, (long long)KVH * W);
+      return (t / W) * U + max(0ll, t % W - PC);
+    };
+    int n = (int)(before(hi) - before(lo));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+    n_units += n;
+  }
+
   // ---- compute-side walker over the pieces of the partition (identical in every warp)
   struct Walker {
-    int b, h, blk;
-    long long seq0;                                // stream position of unit 0 of (b, h)
+    int b, h;
+    long long seq0;                                // stream position of (b, h): PC cost slots, then its units
     ReqInfo r;
   };
   auto seek = [&](Walker& wk, long long pos) {     // move to the sequence that holds pos (pos < total)
     while (true) {
-      const long long end_h = wk.seq0 + wk.r.U;
+      const long long end_h = wk.seq0 + wt(wk.r.U);
       if (pos < end_h) break;
       wk.seq0 = end_h;
       if (++wk.h == KVH) {
@@ -265,19 +303,18 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
         do { wk.r = load_req<LOG_UT>(p, ++wk.b); } while (wk.r.U == 0);
       }
     }
-    wk.blk = (int)(pos - wk.seq0);
   };
   Walker cw;
   cw.b = b0;
   cw.r = load_req<LOG_UT>(p, b0);
-  cw.h = (int)((lo - (long long)base0 * KVH) / cw.r.U);
-  cw.seq0 = (long long)base0 * KVH + (long long)cw.h * cw.r.U;
-  cw.blk = 0;
+  cw.h = (int)((lo - (long long)base0 * KVH) / wt(cw.r.U));
+  cw.seq0 = (long long)base0 * KVH + (long long)cw.h * wt(cw.r.U);
 
   // ---- fetch side: this warp's units are the partition-local indices w, w + TG, ..; the cursor below runs NS units
   // ahead of the compute loop. The common case (next unit in the same sequence, its page ids already in the warp's
   // 32-entry window) costs a shuffle per 16 tokens, one 64-bit multiply-add and the copy instructions of UB lanes.
   const int n_my = n_units > w ? (n_units - w + TG - 1) / TG : 0;
+  const int n_tok = __ldg(p.qsl + B);              // query rows of the batch (bounds the query prefetch)
   // shared-memory addresses of this warp's ring and barriers, and the byte offsets of this lane's rows and blocks
   // inside a stage. They are constant for the whole kernel; passing them through an empty asm keeps the compiler from
   // re-deriving them from the thread index inside the main loop.
@@ -292,7 +329,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
                 VR11 = Gm::tok(9) - Gm::tok(0);                           // t01 - t00, t10 - t00, t11 - t00 (for every c)
 
   int f_b = cw.b, f_h = cw.h, f_U = cw.r.U, f_L = cw.r.L;
-  int f_blk = w + (int)(lo - cw.seq0);              // unit (inside the cursor's sequence) to fetch next; may run past
+  int f_blk = w + (int)max(0ll, lo - cw.seq0 - PC);  // unit (inside the cursor's sequence) to fetch next; may run past
   int f_fast_end = 0;                               // units below this bound take the fast path
   int f_idx = 0, pg = 0;                            // page ids of the warp's next 32 blocks of the sequence, one per lane
   unsigned f_n = 0;                                 // units fetched so far (of n_my)
@@ -398,22 +435,39 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
 
   // ---- compute side: walk the pieces of the partition
   long long pos = lo;
-  int piece_idx = 0;
+  int piece_idx = 0, k_units = 0;                   // pieces and units of the partition dealt with so far
   while (pos < hi) {
     seek(cw, pos);
-    const int blk0 = cw.blk;
-    const long long seq_end = cw.seq0 + cw.r.U;
-    const long long piece_end = min(hi, seq_end);
-    const int n_piece = (int)(piece_end - pos);
-    const int k0 = (int)(pos - lo);                 // partition-local index of the piece's first unit
+    // the sequence's units occupy [seq0 + PC, seq_end); the part of them inside [pos, hi) is this partition's piece
+    const long long seq_u0 = cw.seq0 + PC, seq_end = seq_u0 + cw.r.U;
+    const long long piece_lo = max(pos, seq_u0), piece_end = min(hi, seq_end);
+    if (piece_lo >= piece_end) {                    // only cost slots of this sequence lie in the partition
+      pos = min(hi, seq_end);
+      continue;
+    }
+    const int blk0 = (int)(piece_lo - seq_u0);
+    const int n_piece = (int)(piece_end - piece_lo);
+    const int k0 = k_units;                         // partition-local index of the piece's first unit
+    k_units += n_piece;
     const int b = cw.b, h = cw.h, L = cw.r.L, ql = cw.r.ql, q0 = cw.r.q0, G = p.G;
     const int R = min(RPAD, G * ql - p.row0);      // query rows of this pass: rows row0 .. row0 + R - 1 of the group
     const bool complete = blk0 == 0 && piece_end == seq_end;
+    if (HKV_QPREFETCH && w == 0 && piece_end < hi) {
+      // the partition goes on with the next sequence: ask for its query rows now (L2 prefetch, no registers held), so
+      // that their load latency passes behind this piece instead of stalling all four warps at the start of the next
+      long long row;                                 // first query row of the next sequence (clamped into the tensor)
+      if (h + 1 < KVH) row = (long long)q0 * (KVH * G) + (h + 1) * G;
+      else row = (long long)min(q0 + ql, n_tok - 1) * (KVH * G);
+      const char* a = reinterpret_cast<const char*>(p.q + row * D) + lane * 128;
+      if (lane * 128 < G * D * 2) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+    }
     if (piece_idx == 0 && tid == 0) {
       PartDesc d;
       d.b = b; d.h = h; d.blk_begin = blk0; d.blk_end = blk0 + n_piece; d.units = cw.r.U;
-      d.first_part = (int)(cw.seq0 / per);
-      d.first_slot = cw.seq0 == (long long)d.first_part * per ? 0 : 1;
+      // the partition that holds the sequence's first unit; the piece there is that partition's first piece (slot 0)
+      // iff the partition starts inside this sequence, else an earlier sequence's units come first (slot 1)
+      d.first_part = (int)(seq_u0 / per);
+      d.first_slot = (long long)d.first_part * per >= cw.seq0 ? 0 : 1;
       d.pad = 0;
       descs[part] = d;
     }
@@ -771,6 +825,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
     pos = piece_end;
     ++piece_idx;
   }
+  if (piece_idx == 0 && tid == 0) descs[part].b = -1;   // the partition holds cost slots only
 
   // a warp that gave up may still have copies in flight: wait for them (bounded) before the CTA's shared memory is
   // released
