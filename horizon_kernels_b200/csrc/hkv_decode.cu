@@ -31,8 +31,8 @@
 
 // tuning constants (they can be overridden on the command line of the compiler for experiments)
 #ifndef HKV_PC128
-#define HKV_PC128 8
-#define HKV_PC256 12
+#define HKV_PC128 12
+#define HKV_PC256 24
 #endif
 #ifndef HKV_QPREFETCH
 #define HKV_QPREFETCH 1
