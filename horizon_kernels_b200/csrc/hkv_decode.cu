@@ -544,9 +544,9 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
         }
 #pragma unroll
         for (int i = 0; i < NQ / 2; ++i) {
-          float a = fminf(fmaxf(qf[2 * i], -65504.0f), 65504.0f), bq = fminf(fmaxf(qf[2 * i + 1], -65504.0f), 65504.0f);
+          float a = qf[2 * i], bq = qf[2 * i + 1];
           if (flip) { a = -a; bq = -bq; }
-          qa[i >> 1][i & 1] = pack_f16x2(a, bq);
+          qa[i >> 1][i & 1] = pack_f16x2_sat(a, bq);   // values beyond f16's range become +-65504
         }
       }
       // visible context of query rows 2c, 2c+1 (causal among the request's own query tokens)
@@ -796,28 +796,42 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       __syncthreads();
       const float gvh = __ldg(p.gv + h);
       const int slot_id = part * 2 + (piece_idx == 0 ? 0 : 1);
-      for (int idx = tid; idx < R * (D / 2); idx += NTHREADS) {
-        const int row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
+      // a thread stays on one query row (4 rows x 32 threads, or 8 x 16), so the warps' weights are worked out once
+      const int tpr = R <= RPAD / 2 ? NTHREADS / (RPAD / 2) : NTHREADS / RPAD;   // threads per row
+      const int row = tid / tpr;
+      if (row < R) {
         float mx = -3.0e38f;
 #pragma unroll
         for (int ww = 0; ww < TG; ++ww) mx = fmaxf(mx, mbuf[ww * RPAD + row]);
-        float den = 0.0f, n0 = 0.0f, n1 = 0.0f;
+        float den = 0.0f, wgt[TG];
 #pragma unroll
         for (int ww = 0; ww < TG; ++ww) {
-          const float wgt = fast_exp2(mbuf[ww * RPAD + row] - mx);
-          den += lbuf[ww * RPAD + row] * wgt;
-          const float2 v = *reinterpret_cast<const float2*>(obuf + ((size_t)ww * RPAD + row) * Sm::OROW + ch);
-          n0 += v.x * wgt;
-          n1 += v.y * wgt;
+          wgt[ww] = fast_exp2(mbuf[ww * RPAD + row] - mx);
+          den += lbuf[ww * RPAD + row] * wgt[ww];
         }
         const float inv = den > 0.0f ? gvh / den : 0.0f;
+        const float* orow = obuf + (size_t)row * Sm::OROW;
+        float* dst_p = nullptr;
+        __nv_bfloat16* dst_o = nullptr;
         if (complete) {
           const int t = (p.row0 + row) / G, gq = p.row0 + row - t * G;
-          __nv_bfloat16* dst = p.out + ((long long)(q0 + t) * (KVH * G) + h * G + gq) * D + ch;
-          *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(n0 * inv * p.v_scale, n1 * inv * p.v_scale);
+          dst_o = p.out + ((long long)(q0 + t) * (KVH * G) + h * G + gq) * D;
         } else {
-          *reinterpret_cast<float2*>(opart_ws + ((size_t)slot_id * RPAD + row) * D + ch) = make_float2(n0 * inv, n1 * inv);
-          if (ch == 0) lse_ws[slot_id * RPAD + row] = den > 0.0f ? log2f(den) + mx : -__int_as_float(0x7f800000);
+          dst_p = opart_ws + ((size_t)slot_id * RPAD + row) * D;
+          if (tid == row * tpr) lse_ws[slot_id * RPAD + row] = den > 0.0f ? log2f(den) + mx : -__int_as_float(0x7f800000);
+        }
+        for (int ch = (tid - row * tpr) * 2; ch < D; ch += 2 * tpr) {
+          float n0 = 0.0f, n1 = 0.0f;
+#pragma unroll
+          for (int ww = 0; ww < TG; ++ww) {
+            const float2 v = *reinterpret_cast<const float2*>(orow + (size_t)ww * RPAD * Sm::OROW + ch);
+            n0 += v.x * wgt[ww];
+            n1 += v.y * wgt[ww];
+          }
+          if (complete)
+            *reinterpret_cast<__nv_bfloat162*>(dst_o + ch) = __floats2bfloat162_rn(n0 * inv * p.v_scale, n1 * inv * p.v_scale);
+          else
+            *reinterpret_cast<float2*>(dst_p + ch) = make_float2(n0 * inv, n1 * inv);
         }
       }
       __syncthreads();
