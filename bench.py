@@ -554,7 +554,7 @@ def main():
 
 # DRAM bytes (read + written) per algorithmic byte of one decode launch, from the ncu captures summarised under
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over sum(L) * KVH * D * 1.125)
-TRAFFIC_RATIO = {"c1": (330.12 + 4.80) / 328.42, "c2": (1209.756 + 4.055) / 1207.960}
+TRAFFIC_RATIO = {"c1": (330.123 + 4.825) / 328.42, "c2": (1209.754 + 4.464) / 1207.960}
 
 if __name__ == "__main__":
     main()
