@@ -7,9 +7,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libhkv.so")
 
 EXPORTS = ("hkv_version", "hkv_error_string", "hkv_last_cuda_error", "hkv_write", "hkv_decode_workspace_bytes",
-           "hkv_decode", "hkv_combine", "hkv_workspace_status", "hkv_decode_noalloc", "hkv_set_option", "hkv_dequant", "hkv_write_rot",
+           "hkv_decode", "hkv_combine", "hkv_workspace_status", "hkv_decode_noalloc", "hkv_decode_noalloc_status",
+           "hkv_set_option", "hkv_dequant", "hkv_write_rot",
            "hkv_decode_rot", "hkv_write_k8", "hkv_decode_k8", "hkv_dequant_k8",
-           "hkv_selftest_wait_timeout")
+           "hkv_selftest_wait_timeout", "hkv_selftest_codec")
 
 _lib = None
 
@@ -49,6 +50,8 @@ def load():
         L.hkv_decode_noalloc.restype = i32
         L.hkv_decode_noalloc.argtypes = [vp, vp, vp, vp, vp, C.POINTER(i64), i32, vp, i32, vp, vp, i32, i32, i32, i32, i32,
                                          f32, f32, vp, vp, i32, vp, vp]
+        L.hkv_decode_noalloc_status.restype = i32
+        L.hkv_decode_noalloc_status.argtypes = [C.POINTER(i32), vp]
         L.hkv_write_rot.restype = i32
         L.hkv_write_rot.argtypes = L.hkv_write.argtypes[:-1] + [vp, vp]
         L.hkv_decode_rot.restype = i32
@@ -67,6 +70,8 @@ def load():
                                      i32, vp]
         L.hkv_selftest_wait_timeout.restype = i32
         L.hkv_selftest_wait_timeout.argtypes = [vp, i64, vp]
+        L.hkv_selftest_codec.restype = i32
+        L.hkv_selftest_codec.argtypes = [vp, C.c_size_t, vp]
         L.hkv_set_option.restype = i32
         L.hkv_set_option.argtypes = [i32, i32]
         L.hkv_workspace_status.restype = i32

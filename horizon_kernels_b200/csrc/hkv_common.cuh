@@ -12,26 +12,14 @@ namespace hkv {
 
 // ---------------------------------------------------------------------------------------------------- workspace
 // Layout of the decode workspace (all offsets from the 256-byte aligned base):
-//   Header | PartDesc[n_parts] | lse[n_parts][2][RPAD] fp32 | opart[n_parts][2][RPAD][D] fp32
+//   Header | tickets[n_parts] int | lse[n_parts][2][RPAD] fp32 | opart[n_parts][2][RPAD][D] fp32
 // Each decode partition (one CTA) owns two partial slots: slot 0 for a sequence piece that begins the partition,
-// slot 1 for a piece that ends it while the sequence continues in the next partition.
+// slot 1 for a piece that ends it while the sequence continues in the next partition. tickets[p] counts the finished
+// pieces of the split sequence that ENDS in partition p; the CTA that brings it to the number of pieces merges them
+// and sets it back to zero, so the counters are zero between launches (the workspace starts zero-filled).
 struct Header {
   int status;      // HKV_OK or HKV_ERR_DEVICE_WAIT, set by a kernel whose bounded wait ran out
-  int n_parts;     // partitions used by the last decode launch
-  int per;         // stream units (16-token blocks of one kv head) per partition
-  int total;       // stream units in total
-  int pad[12];
-};
-
-struct PartDesc {
-  int b;           // request of the partition's first piece (-1: the partition is empty)
-  int h;           // kv head of that piece
-  int blk_begin;   // first 16-token block of the piece inside its sequence
-  int blk_end;     // one past its last block
-  int units;       // blocks in the whole sequence (per kv head)
-  int first_part;  // partition holding the sequence's first block
-  int first_slot;  // partial slot used by that first partition for this sequence (0 or 1)
-  int pad;
+  int pad[15];
 };
 
 constexpr int kMaxBatch = 8192;          // requests per decode call (coarse prefix table lives in shared memory)
@@ -40,10 +28,10 @@ constexpr long long kWaitCycles = 1ll << 32;   // bound of every device-side wai
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-  size_t desc_off, lse_off, opart_off, total;
+  size_t ticket_off, lse_off, opart_off, total;
   __host__ __device__ WorkspaceLayout(int n_parts, int rpad, int D) {
-    desc_off = align_up(sizeof(Header), 256);
-    lse_off = align_up(desc_off + sizeof(PartDesc) * (size_t)n_parts, 256);
+    ticket_off = align_up(sizeof(Header), 256);
+    lse_off = align_up(ticket_off + sizeof(int) * (size_t)n_parts, 256);
     opart_off = align_up(lse_off + sizeof(float) * (size_t)n_parts * 2 * rpad, 256);
     total = align_up(opart_off + sizeof(float) * (size_t)n_parts * 2 * rpad * D, 256);
   }

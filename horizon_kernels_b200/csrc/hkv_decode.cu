@@ -5,8 +5,10 @@
 // is cut into equal partitions, one per CTA of a grid that fills the GPU exactly once. A CTA therefore streams the same
 // number of cache bytes as every other CTA whatever the mix of context lengths. Inside a partition, a run of units of
 // the same (request, kv head) is a *piece*. A piece that covers its whole sequence is finished by the CTA and written
-// to the output; other pieces leave a normalised fp32 partial and a log2-sum-exp in the workspace, which the combine
-// kernel merges in partition order (fixed order => deterministic results).
+// to the output; other pieces leave a normalised fp32 partial and a log2-sum-exp in the workspace. The log-sum-exp
+// combine of a split sequence runs inside the same launch: every CTA that wrote a piece of it draws a ticket from a
+// per-sequence counter when it is done, and the CTA that draws the last ticket merges all pieces in partition order
+// (fixed order => deterministic results, whoever merges). No CTA ever waits for another one.
 //
 // Inside a CTA, TG warps take the partition's units round-robin. Every warp owns a private ring of NS shared-memory
 // stages; it issues 1-D bulk copies (cp.async.bulk, completion on an mbarrier) for its own future units, driven by
@@ -25,25 +27,15 @@
 
 #include <algorithm>
 #include <atomic>
+#include <mutex>
 #include <cmath>
 
 #include "hkv_common.cuh"
 
-// tuning constants (they can be overridden on the command line of the compiler for experiments)
-#ifndef HKV_PC128
-#define HKV_PC128 12
-#define HKV_PC256 24
-#endif
-#ifndef HKV_QPREFETCH
-#define HKV_QPREFETCH 1
-#endif
-
 namespace hkv {
 
-#ifndef HKV_TG
-#define HKV_TG 4
-#endif
-constexpr int TG = HKV_TG;       // consumer warps per CTA
+constexpr int TG = 4;            // consumer warps per CTA
+constexpr bool kQueryPrefetch = true;   // ask for the next sequence's query rows (L2 prefetch) while a piece is computed
 constexpr int NTHREADS = TG * 32;
 constexpr int RPAD = 8;          // query rows per (request, kv head) of one pass, padded to the mma N tile
 constexpr int kMaxRows = 64;     // G * qlmax: more than RPAD rows are served by several passes over the cache
@@ -87,13 +79,8 @@ struct Geo {
   static constexpr int SD = D / 2, SS = D / 16, SLOT = SD + SS;
   static constexpr int UB = D == 128 ? 2 : 1;          // 16-token blocks per unit
   static constexpr int UT = 16 * UB, LOG_UT = UB == 2 ? 5 : 4;
-#ifndef HKV_NS128
-#define HKV_NS128 3
-#define HKV_MINB128 3
-#endif
-
-  static constexpr int NS = D == 128 ? HKV_NS128 : LAYOUT == 2 ? 3 : 4;   // stages per warp
-  static constexpr int MINB = D == 128 ? HKV_MINB128 : 2;   // CTAs per SM the register budget is sized for
+  static constexpr int NS = D == 128 ? 3 : LAYOUT == 2 ? 3 : 4;   // stages per warp
+  static constexpr int MINB = D == 128 ? 3 : 2;        // CTAs per SM the register budget is sized for
   static constexpr bool K8 = LAYOUT == 2;
   static constexpr int SLOT8 = D + SD + SS;            // K8V4 slot: 400 bytes at head_dim 256
   static constexpr int TILE = UT * SLOT;               // bytes of one (head, side) tile of a unit
@@ -107,14 +94,11 @@ struct Geo {
   // What a sequence costs a partition beyond its units (locating it, loading its queries, the end-of-piece merge and
   // the output), in units: measured 3 to 4 microseconds per piece. The stream that is cut into equal partitions counts
   // every sequence as PIECE_COST + its units, so partitions that hold many short sequences get fewer units.
-  static constexpr int PIECE_COST = D == 128 ? HKV_PC128 : HKV_PC256;
+  static constexpr int PIECE_COST = D == 128 ? 12 : 24;
   static constexpr int KS = D / 16;                    // k-steps of K Q^T == mma tiles of V^T P^T (per 16 tokens)
   static constexpr int NBL = D / 64;                   // 16-channel blocks of one key row held by one lane
   static constexpr int NH = D / 128;                   // 16-channel blocks of one value row held by one lane
-#ifndef HKV_NCH128
-#define HKV_NCH128 1
-#endif
-  static constexpr int NCH = UB == 1 ? 2 : HKV_NCH128; // independent accumulators per score tile
+  static constexpr int NCH = UB == 1 ? 2 : 1;          // independent accumulators per score tile
   // token (row of a 16-token block) handled by row i of the 16-row score tile. With 72-byte rows (head_dim 128, slot
   // layout) bits 1 and 3 of i are swapped: then the key loads of a half warp (rows i = 4k .. 4k+3, 16 bytes apart
   // inside a row) and its value loads (rows i = j, j+2, j+4, j+6, 32 contiguous bytes of each) both touch every
@@ -144,6 +128,75 @@ __device__ __forceinline__ ReqInfo load_req(const DecodeParams& p, int b) {
   return r;
 }
 
+// a split sequence as the ticket round at the end of a partition needs it
+struct SplitSeq {
+  int b, h, U;                                       // request, kv head, units of the whole sequence
+  long long seq0;                                    // stream position of the sequence (its cost slots come first)
+};
+
+// ------------------------------------------------------------------------------------------------------- combine
+// Log-sum-exp merge of the pieces of one split sequence, run by the whole CTA that drew the sequence's last ticket.
+// The pieces live in slot `first_slot` of partition `first`, and in slot 0 of every later partition up to `last`.
+// w_i = 2^(lse_i - max) / sum, accumulated in partition order with a running maximum, so the result does not depend
+// on which CTA merges. out_row points at row 0 of the (request, kv head) group's first query token; rows of the next
+// token are tok_stride elements further. (Reference: hz4::combine_rg, kv_fp4_serving.py:518-558.)
+template <int D>
+__device__ __forceinline__ void merge_split(const float* lse_ws, const float* opart_ws, int first, int last,
+                                            int first_slot, int R, int row0, int G, __nv_bfloat16* out_row,
+                                            long long tok_stride, float v_scale) {
+  constexpr int IT = RPAD * (D / 2) / NTHREADS;      // (row, channel pair) items per thread
+  constexpr int GRP = 4;                             // pieces per round: GRP * IT independent loads in flight
+  const float ninf = -__int_as_float(0x7f800000);
+  float mx[IT], tot[IT], n0[IT], n1[IT];
+#pragma unroll
+  for (int it = 0; it < IT; ++it) { mx[it] = ninf; tot[it] = n0[it] = n1[it] = 0.0f; }
+  for (int pc0 = first; pc0 <= last; pc0 += GRP) {
+    float ls[IT][GRP];
+    float2 v[IT][GRP];
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+      const int idx = threadIdx.x + it * NTHREADS, row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
+#pragma unroll
+      for (int i = 0; i < GRP; ++i) {
+        const int pc = pc0 + i;
+        const int slot = pc * 2 + (pc == first ? first_slot : 0);
+        const bool on = pc <= last && row < R;
+        ls[it][i] = on ? __ldcg(lse_ws + slot * RPAD + row) : ninf;
+        v[it][i] = on ? __ldcg(reinterpret_cast<const float2*>(opart_ws + ((size_t)slot * RPAD + row) * D + ch))
+                      : make_float2(0.f, 0.f);
+      }
+    }
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+      float gm = ls[it][0];
+#pragma unroll
+      for (int i = 1; i < GRP; ++i) gm = fmaxf(gm, ls[it][i]);
+      if (gm == ninf) continue;                      // only empty pieces in this round
+      const float nm = fmaxf(mx[it], gm);
+      const float keep = mx[it] == ninf ? 0.0f : exp2f(mx[it] - nm);
+      tot[it] *= keep; n0[it] *= keep; n1[it] *= keep;
+      mx[it] = nm;
+#pragma unroll
+      for (int i = 0; i < GRP; ++i) {
+        if (ls[it][i] == ninf) continue;             // an empty piece: its partial is garbage and must not be used
+        const float wgt = exp2f(ls[it][i] - nm);
+        tot[it] += wgt;
+        n0[it] += v[it][i].x * wgt;
+        n1[it] += v[it][i].y * wgt;
+      }
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < IT; ++it) {
+    const int idx = threadIdx.x + it * NTHREADS, row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
+    if (row >= R) continue;
+    const float inv = tot[it] > 0.0f ? v_scale / tot[it] : 0.0f;
+    const int t = (row0 + row) / G, gq = row0 + row - t * G;
+    *reinterpret_cast<__nv_bfloat162*>(out_row + t * tok_stride + (long long)gq * D + ch) =
+        __floats2bfloat162_rn(n0[it] * inv, n1[it] * inv);
+  }
+}
+
 template <int D, int LAYOUT>
 struct Smem {
   using G_ = Geo<D, LAYOUT>;
@@ -167,13 +220,16 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   float* mbuf = obuf + TG * RPAD * Sm::OROW;
   float* lbuf = mbuf + TG * RPAD;
   int* coarse = reinterpret_cast<int*>(smem + Sm::RING + Sm::BARS + Sm::MERGE);
+  __shared__ SplitSeq split[2];
+  __shared__ int split_win[2];
+  unsigned pending = 0;                             // bit 0 / 1: the partition's first / last piece belongs to a split sequence
 
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, c = lane & 3;
   const int KVH = p.KVH, B = p.B;
   Header* hdr = reinterpret_cast<Header*>(p.ws);
   const int n_parts = gridDim.x, part = blockIdx.x;
   const WorkspaceLayout wl(n_parts, RPAD, D);
-  PartDesc* descs = reinterpret_cast<PartDesc*>(p.ws + wl.desc_off);
+  int* tickets = reinterpret_cast<int*>(p.ws + wl.ticket_off);
   float* lse_ws = reinterpret_cast<float*>(p.ws + wl.lse_off);
   float* opart_ws = reinterpret_cast<float*>(p.ws + wl.opart_off);
 
@@ -230,14 +286,6 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   if (lo >= hi) {                                   // an idle partition
     if (early) pdl_wait();
     pdl_launch_dependents();
-    if (tid == 0) {
-      if (part == 0) {
-        hdr->n_parts = n_parts;
-        hdr->per = per;
-        hdr->total = (int)total;
-      }
-      descs[part].b = -1;
-    }
     return;
   }
 
@@ -412,11 +460,6 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
 
   if (early) pdl_wait();                            // from here on: workspace writes, block tables, cache and query reads
   pdl_launch_dependents();
-  if (part == 0 && tid == 0) {
-    hdr->n_parts = n_parts;
-    hdr->per = per;
-    hdr->total = (int)total;
-  }
 
   unsigned c_n = 0;                                 // stages consumed so far
   uint32_t c_bar = bars_a, c_st = ring_a, c_par = 0;  // barrier, stage and phase parity of the next stage to consume
@@ -452,7 +495,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
     const int b = cw.b, h = cw.h, L = cw.r.L, ql = cw.r.ql, q0 = cw.r.q0, G = p.G;
     const int R = min(RPAD, G * ql - p.row0);      // query rows of this pass: rows row0 .. row0 + R - 1 of the group
     const bool complete = blk0 == 0 && piece_end == seq_end;
-    if (HKV_QPREFETCH && w == 0 && piece_end < hi) {
+    if (kQueryPrefetch && w == 0 && piece_end < hi) {
       // the partition goes on with the next sequence: ask for its query rows now (L2 prefetch, no registers held), so
       // that their load latency passes behind this piece instead of stalling all four warps at the start of the next
       long long row;                                 // first query row of the next sequence (clamped into the tensor)
@@ -461,16 +504,13 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       const char* a = reinterpret_cast<const char*>(p.q + row * D) + lane * 128;
       if (lane * 128 < G * D * 2) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
     }
-    if (piece_idx == 0 && tid == 0) {
-      PartDesc d;
-      d.b = b; d.h = h; d.blk_begin = blk0; d.blk_end = blk0 + n_piece; d.units = cw.r.U;
-      // the partition that holds the sequence's first unit; the piece there is that partition's first piece (slot 0)
-      // iff the partition starts inside this sequence, else an earlier sequence's units come first (slot 1)
-      d.first_part = (int)(seq_u0 / per);
-      d.first_slot = (long long)d.first_part * per >= cw.seq0 ? 0 : 1;
-      d.pad = 0;
-      descs[part] = d;
+    if (!complete && tid == 0) {
+      // a piece of a split sequence: remember the sequence for the ticket round at the end of the partition (at most
+      // two per partition: its first piece and, when the last sequence runs on into the next partition, its last)
+      SplitSeq& sq = split[piece_idx == 0 ? 0 : 1];
+      sq.b = b; sq.h = h; sq.U = cw.r.U; sq.seq0 = cw.seq0;
     }
+    if (!complete) pending |= piece_idx == 0 ? 1u : 2u;
 
     // this warp's units of the piece: blk_first, blk_first + TG, .. < blk_end
     const int blk_first = blk0 + ((w - k0) % TG + TG) % TG, blk_end = blk0 + n_piece;
@@ -839,7 +879,41 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
     pos = piece_end;
     ++piece_idx;
   }
-  if (piece_idx == 0 && tid == 0) descs[part].b = -1;   // the partition holds cost slots only
+
+  // ---- ticket round of the split sequences this partition holds a piece of: the CTA that finishes a sequence's last
+  // outstanding piece merges all of them (log-sum-exp weights, partition order) and writes the output rows. The
+  // partial was written by many threads: each makes its own writes visible device-wide, the CTA barrier orders them
+  // before the thread that draws the ticket, and the merging CTA reads the partials past the L1 (ld.global.cg).
+  if (pending) {
+    __threadfence();
+    __syncthreads();
+    if (tid < 2) {
+      int win = 0;
+      if (pending >> tid & 1u) {
+        const SplitSeq sq = split[tid];
+        const long long seq_u0 = sq.seq0 + PC;
+        const int first = (int)(seq_u0 / per), last = (int)((seq_u0 + sq.U - 1) / per);
+        __threadfence();
+        const int old = atomicAdd(tickets + last, 1);
+        win = old == last - first;
+        if (win) tickets[last] = 0;                  // every piece has arrived: nobody touches the counter again
+      }
+      split_win[tid] = win;
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int i = 0; i < 2; ++i) {
+      if (!split_win[i]) continue;
+      __threadfence();
+      const SplitSeq sq = split[i];
+      const long long seq_u0 = sq.seq0 + PC;
+      const int first = (int)(seq_u0 / per), last = (int)((seq_u0 + sq.U - 1) / per);
+      const int first_slot = (long long)first * per >= sq.seq0 ? 0 : 1;
+      const ReqInfo r = load_req<LOG_UT>(p, sq.b);
+      merge_split<D>(lse_ws, opart_ws, first, last, first_slot, min(RPAD, p.G * r.ql - p.row0), p.row0, p.G,
+                     p.out + ((long long)r.q0 * (KVH * p.G) + sq.h * p.G) * D, (long long)KVH * p.G * D, p.v_scale);
+    }
+  }
 
   // a warp that gave up may still have copies in flight: wait for them (bounded) before the CTA's shared memory is
   // released
@@ -851,81 +925,16 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   }
 }
 
-// ------------------------------------------------------------------------------------------------------- combine
-// One CTA per decode partition. A partition whose FIRST piece ends a sequence that began in an earlier partition
-// merges that sequence: pieces live in slot `first_slot` of partition `first_part`, slot 0 of every partition in
-// between, and slot 0 of this one. Weights w_i = 2^(lse_i - max) / sum, summed in partition order.
-template <int D>
-__global__ void __launch_bounds__(128) combine_kernel(const uint8_t* ws, const int* qsl, __nv_bfloat16* out, int KVH,
-                                                      int G, int qlmax, int row0, float v_scale) {
-  const int part = blockIdx.x, tid = threadIdx.x;
-  pdl_wait();                                     // the workspace is written by the preceding decode launch
-  pdl_launch_dependents();
-  // the descriptor table sits at a fixed offset, so its load does not wait for the header's
-  const PartDesc d = reinterpret_cast<const PartDesc*>(ws + align_up(sizeof(Header), 256))[part < 0 ? 0 : part];
-  const int n_parts = reinterpret_cast<const Header*>(ws)->n_parts;
-  if (part >= n_parts) return;
-  if (d.b < 0 || d.blk_begin == 0 || d.blk_end != d.units) return;
-  const WorkspaceLayout wl(n_parts, RPAD, D);
-  const float* lse_ws = reinterpret_cast<const float*>(ws + wl.lse_off);
-  const float* opart_ws = reinterpret_cast<const float*>(ws + wl.opart_off);
-  const int q0 = qsl[d.b];
-  int ql = qsl[d.b + 1] - q0;
-  ql = (ql < 0 || ql > qlmax) ? 0 : ql;
-  const int R = min(RPAD, G * ql - row0);           // rows row0 .. row0 + R - 1 of the group were computed by this pass
-  const float ninf = -__int_as_float(0x7f800000);
-  const int first = d.first_part, first_slot = d.first_slot;
-  constexpr int GRP = 8;                            // pieces merged per round: their loads are independent
-  for (int idx = tid; idx < R * (D / 2); idx += 128) {
-    const int row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
-    // a running maximum carries the log-sum-exp weights from round to round (fixed order => deterministic)
-    float mx = ninf, tot = 0.0f, n0 = 0.0f, n1 = 0.0f;
-    for (int pc0 = first; pc0 <= part; pc0 += GRP) {
-      float ls[GRP];
-      float2 v[GRP];
-#pragma unroll
-      for (int i = 0; i < GRP; ++i) {
-        const int pc = pc0 + i;
-        const int slot = pc * 2 + (pc == first ? first_slot : 0);
-        const bool on = pc <= part;
-        ls[i] = on ? lse_ws[slot * RPAD + row] : ninf;
-        v[i] = on ? *reinterpret_cast<const float2*>(opart_ws + ((size_t)slot * RPAD + row) * D + ch) : make_float2(0.f, 0.f);
-      }
-      float gm = ls[0];
-#pragma unroll
-      for (int i = 1; i < GRP; ++i) gm = fmaxf(gm, ls[i]);
-      if (gm == ninf) continue;                      // only empty pieces in this round
-      const float nm = fmaxf(mx, gm);
-      const float keep = mx == ninf ? 0.0f : exp2f(mx - nm);
-      tot *= keep; n0 *= keep; n1 *= keep;
-      mx = nm;
-#pragma unroll
-      for (int i = 0; i < GRP; ++i) {
-        if (ls[i] == ninf) continue;                 // an empty piece: its partial is garbage and must not be used
-        const float wgt = exp2f(ls[i] - nm);
-        tot += wgt;
-        n0 += v[i].x * wgt;
-        n1 += v[i].y * wgt;
-      }
-    }
-    {
-      const float inv = tot > 0.0f ? v_scale / tot : 0.0f;
-      const int t = (row0 + row) / G, gq = row0 + row - t * G;
-      __nv_bfloat16* dst = out + ((long long)(q0 + t) * (KVH * G) + d.h * G + gq) * D + ch;
-      *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(n0 * inv, n1 * inv);
-    }
-  }
-}
-
 // ----------------------------------------------------------------------------------------------------- host side
 int record_cuda(cudaError_t e);
 
 struct DeviceInfo {
   int sms = 0;
   int ctas_per_sm[2][3] = {{0, 0, 0}, {0, 0, 0}};    // [D == 256][LAYOUT]
-  bool ready = false;
+  std::atomic<bool> ready{false};                    // set (release) after the fields above, under g_setup_mutex
 };
 static DeviceInfo g_dev[64];
+static std::mutex g_setup_mutex;                     // serialises the once-per-device set-up of concurrent host threads
 static std::atomic<int> g_early_metadata{0};
 
 template <int D, int LAYOUT>
@@ -942,15 +951,18 @@ static int device_info(DeviceInfo** out) {
   if (e != cudaSuccess) return record_cuda(e);
   if (dev < 0 || dev >= 64) return HKV_ERR_RANGE;
   DeviceInfo& di = g_dev[dev];
-  if (!di.ready) {
-    e = cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return record_cuda(e);
-    if ((e = setup_variant<128, 0>(di.ctas_per_sm[0][0])) != cudaSuccess) return record_cuda(e);
-    if ((e = setup_variant<128, 1>(di.ctas_per_sm[0][1])) != cudaSuccess) return record_cuda(e);
-    if ((e = setup_variant<256, 0>(di.ctas_per_sm[1][0])) != cudaSuccess) return record_cuda(e);
-    if ((e = setup_variant<256, 1>(di.ctas_per_sm[1][1])) != cudaSuccess) return record_cuda(e);
-    if ((e = setup_variant<256, 2>(di.ctas_per_sm[1][2])) != cudaSuccess) return record_cuda(e);
-    di.ready = true;
+  if (!di.ready.load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    if (!di.ready.load(std::memory_order_relaxed)) {
+      e = cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return record_cuda(e);
+      if ((e = setup_variant<128, 0>(di.ctas_per_sm[0][0])) != cudaSuccess) return record_cuda(e);
+      if ((e = setup_variant<128, 1>(di.ctas_per_sm[0][1])) != cudaSuccess) return record_cuda(e);
+      if ((e = setup_variant<256, 0>(di.ctas_per_sm[1][0])) != cudaSuccess) return record_cuda(e);
+      if ((e = setup_variant<256, 1>(di.ctas_per_sm[1][1])) != cudaSuccess) return record_cuda(e);
+      if ((e = setup_variant<256, 2>(di.ctas_per_sm[1][2])) != cudaSuccess) return record_cuda(e);
+      di.ready.store(true, std::memory_order_release);
+    }
   }
   *out = &di;
   return HKV_OK;
@@ -1048,19 +1060,11 @@ static int decode_impl(const void* q, const void* kd, const void* ksf, const voi
                                      : layout == 2 ? (size_t)Smem<256, 2>::TOTAL : (size_t)Smem<256, 0>::TOTAL;
   static_assert(Smem<128, 0>::TOTAL == Smem<128, 1>::TOTAL && Smem<256, 0>::TOTAL == Smem<256, 1>::TOTAL, "layouts share a size");
   // More than RPAD query rows per kv head (large groups, several draft tokens) are served RPAD rows at a time: every
-  // pass is a decode launch over the cache plus its combine; the last pass's combine is left to hkv_combine.
-  void (*kc)(const uint8_t*, const int*, __nv_bfloat16*, int, int, int, int, float) =
-      D == 128 ? combine_kernel<128> : combine_kernel<256>;
-  const unsigned cgrid = (unsigned)max_parts(*di, D);
+  // pass is one launch over the cache (split sequences are merged inside it).
   for (int row0 = 0; row0 < G * qlmax; row0 += RPAD) {
     p.row0 = row0;
     rc = record_cuda(launch_pdl(k, dim3(grid), dim3(NTHREADS), smem_bytes, st, p));
     if (rc != HKV_OK) return rc;
-    if (row0 + RPAD < G * qlmax) {
-      rc = record_cuda(launch_pdl(kc, dim3(cgrid), dim3(128), 0, st, (const uint8_t*)workspace,
-                                  (const int*)query_start_loc, (__nv_bfloat16*)out, KVH, G, qlmax, row0, v_scale));
-      if (rc != HKV_OK) return rc;
-    }
   }
   return HKV_OK;
 }
@@ -1097,26 +1101,18 @@ extern "C" int hkv_decode_k8(const void* q, const void* kd, const void* vd, cons
 extern "C" int hkv_combine(const void* workspace, size_t workspace_bytes, const int32_t* query_start_loc, int B,
                            int KVH, int G, int D, int qlmax, float v_scale, void* out, void* stream) {
   using namespace hkv;
+  // The log-sum-exp combine runs inside the decode launch (merge_split above): when hkv_decode's kernels have finished,
+  // `out` is complete. This entry point is kept so that callers written against the three-call sequence of the
+  // reference (write, decode, combine) keep working; it checks its arguments like before and launches nothing.
+  (void)v_scale; (void)stream;
   if (B < 0) return HKV_ERR_RANGE;
   if (B == 0) return HKV_OK;
   if (!workspace || !query_start_loc || !out) return HKV_ERR_NULL;
   if (D != 128 && D != 256) return HKV_ERR_UNSUPPORTED;
   if (KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > kMaxRows) return HKV_ERR_UNSUPPORTED;
   if (((uintptr_t)workspace & 255) || ((uintptr_t)out & 15)) return HKV_ERR_ALIGN;
-  if (workspace_bytes < sizeof(Header)) return HKV_ERR_WORKSPACE;
-  DeviceInfo* di;
-  int rc = device_info(&di);
-  if (rc != HKV_OK) return rc;
-  // the grid covers the largest partition count a decode launch can use on this device; the kernel reads the actual
-  // count from the workspace header
-  const unsigned grid = (unsigned)max_parts(*di, D);
   if (workspace_bytes < WorkspaceLayout(1, RPAD, D).total) return HKV_ERR_WORKSPACE;
-  cudaStream_t st = (cudaStream_t)stream;
-  void (*k)(const uint8_t*, const int*, __nv_bfloat16*, int, int, int, int, float) =
-      D == 128 ? combine_kernel<128> : combine_kernel<256>;
-  const int row0 = (G * qlmax - 1) / RPAD * RPAD;     // the last pass of hkv_decode
-  return record_cuda(launch_pdl(k, dim3(grid), dim3(128), 0, st, (const uint8_t*)workspace, (const int*)query_start_loc,
-                                (__nv_bfloat16*)out, KVH, G, qlmax, row0, v_scale));
+  return HKV_OK;
 }
 
 extern "C" int hkv_set_option(int option, int value) {
@@ -1167,7 +1163,7 @@ namespace hkv {
 constexpr size_t kNoAllocScratchBytes = 5u << 20;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 // device address of the array per device ordinal; the symbol's name above is only a host-side handle
-static void* g_noalloc_ptr[64] = {};
+static std::atomic<void*> g_noalloc_ptr[64] = {};
 }  // namespace hkv
 
 extern "C" int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
@@ -1185,12 +1181,12 @@ extern "C" int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return record_cuda(e);
   if (dev < 0 || dev >= 64) return HKV_ERR_RANGE;
-  if (g_noalloc_ptr[dev] == nullptr) {              // set-up, once per device, with that device current
-    void* ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+  void* ws = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (ws == nullptr) {                              // set-up, once per device, with that device current
+    e = cudaGetSymbolAddress(&ws, g_noalloc_scratch);
     if (e != cudaSuccess) return record_cuda(e);
-    if (ptr == nullptr) return HKV_ERR_CUDA;
-    g_noalloc_ptr[dev] = ptr;
+    if (ws == nullptr) return HKV_ERR_CUDA;
+    g_noalloc_ptr[dev].store(ws, std::memory_order_release);   // (two threads racing here store the same address)
   }
   DeviceInfo* di;
   const int rc0 = device_info(&di);
@@ -1201,9 +1197,22 @@ extern "C" int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf
   if (splits > 0) n_parts = std::min<long long>(n_parts, (long long)B * KVH * splits);
   if (n_parts < 1) n_parts = 1;
   if (WorkspaceLayout((int)n_parts, RPAD, D).total > kNoAllocScratchBytes) return HKV_ERR_NOALLOC_LIMIT;
-  void* ws = g_noalloc_ptr[dev];
   const int rc = hkv_decode(q, kd, ksf, vd, vsf, strides, PS, block_tables, MP, seq_lens, query_start_loc, B, KVH, G, D,
                             qlmax, sm_scale, v_scale, gk, gv, ws, kNoAllocScratchBytes, splits, out, stream);
-  if (rc != HKV_OK) return rc;
-  return hkv_combine(ws, kNoAllocScratchBytes, query_start_loc, B, KVH, G, D, qlmax, v_scale, out, stream);
+  return rc;
+}
+
+extern "C" int hkv_decode_noalloc_status(int* status, void* stream) {
+  using namespace hkv;
+  if (!status) return HKV_ERR_NULL;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return record_cuda(e);
+  if (dev < 0 || dev >= 64) return HKV_ERR_RANGE;
+  void* ws = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (ws == nullptr) {                              // no hkv_decode_noalloc call on this device yet: nothing to report
+    *status = HKV_OK;
+    return HKV_OK;
+  }
+  return hkv_workspace_status(ws, status, stream);
 }

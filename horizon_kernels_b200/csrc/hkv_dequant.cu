@@ -69,8 +69,15 @@ __global__ void __launch_bounds__(256) dequant_kernel(const DequantParams p) {
     pos = tok - __ldg(p.cu + lo);
     btrow = p.bt + (long long)__ldg(p.rows + lo) * p.MP;
   }
-  const long long page = __ldg(btrow + pos / p.PS), off = pos % p.PS;
   uint4* dst = reinterpret_cast<uint4*>((side ? p.out_v : p.out_k) + ((tok * p.KVH + h) * (long long)D + blk * 16) / 2);
+  if (pos / p.PS >= p.MP) {
+    // a position beyond the block table's reach (bad packed offsets): never read past the table row; the output rows
+    // of such positions are zero
+    dst[0] = make_uint4(0, 0, 0, 0);
+    dst[1] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const long long page = __ldg(btrow + pos / p.PS), off = pos % p.PS;
   if (K8 && side == 0) {
     const uint4 w8 = *reinterpret_cast<const uint4*>(p.kd + page * p.dsp + off * p.dst + h * p.dsh + blk * 16);
     const uint32_t ws[4] = {w8.x, w8.y, w8.z, w8.w};
@@ -127,6 +134,7 @@ static int dequant_impl(const void* kd, const void* ksf, const void* vd, const v
   if ((strides[0] | strides[1] | strides[2]) & 7) return HKV_ERR_ALIGN;
   if (((uintptr_t)out_k | (uintptr_t)out_v) & 15) return HKV_ERR_ALIGN;
   if (n_tokens > 0x7fffffffll || start + n_tokens > 0x7fffffffll) return HKV_ERR_RANGE;
+  if (cu == nullptr && start + n_tokens > (int64_t)MP * PS) return HKV_ERR_RANGE;   // positions beyond the table row
   DequantParams p;
   p.kd = (const uint8_t*)kd; p.ksf = (const uint8_t*)ksf; p.vd = (const uint8_t*)vd; p.vsf = (const uint8_t*)vsf;
   p.dsp = strides[0]; p.dst = strides[1]; p.dsh = strides[2];

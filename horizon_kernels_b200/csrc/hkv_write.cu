@@ -13,6 +13,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -20,6 +21,8 @@
 #include "hkv_common.cuh"
 
 namespace hkv {
+
+int record_cuda(cudaError_t e);
 
 struct WriteParams {
   const __nv_bfloat16* key;
@@ -338,11 +341,38 @@ __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
   if (cand == 0) (side ? p.vsf : p.ksf)[page * p.ssp + pos * p.sst + h * p.ssh + blk] = (uint8_t)cb;
 }
 
-static int g_last_cuda_error = 0;
+// ---- self-test of the conversions the write and decode kernels rely on (see hkv_selftest_codec in include/hkv.h)
+// counts[0]: non-negative non-NaN fp32 bit patterns (0 .. +inf) whose hardware E2M1 code differs from the threshold
+// chain e2m1_mag; counts[1]: the same among the NaN patterns above +inf.
+__global__ void selftest_e2m1_encode_kernel(unsigned long long* counts) {
+  unsigned long long bad = 0, bad_nan = 0;
+  const unsigned long long step = 2ull * gridDim.x * blockDim.x;
+  for (unsigned long long b = 2ull * (blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x); b < (1ull << 31);
+       b += step) {
+    const float y0 = __uint_as_float((unsigned)b), y1 = __uint_as_float((unsigned)b + 1u);
+    const uint32_t w = e2m1_codes8(y0, y1, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f);
+    const unsigned m0 = (w & 15u) != e2m1_mag(y0), m1 = ((w >> 4) & 15u) != e2m1_mag(y1);
+    if (b <= 0x7f800000ull) bad += m0; else bad_nan += m0;
+    if (b + 1 <= 0x7f800000ull) bad += m1; else bad_nan += m1;
+  }
+  if (bad) atomicAdd(counts, bad);
+  if (bad_nan) atomicAdd(counts + 1, bad_nan);
+}
+// table[code * 256 + scale byte] = f16 bits of cvt.rn.f16x2.e2m1x2(code) * cvt.rn.f16x2.e4m3x2(scale byte), the product
+// the decode and dequantisation kernels form (16 codes x 256 scale bytes)
+__global__ void selftest_decode_table_kernel(uint16_t* table) {
+  const unsigned code = blockIdx.x, sb = threadIdx.x;
+  uint32_t v[4];
+  e2m1x8_to_f16x2(code, v);                        // the code in the low nibble of byte 0: value in the low half of v[0]
+  const uint32_t prod = hmul2(v[0], e4m3x2_to_f16x2(sb));
+  table[code * 256 + sb] = (uint16_t)(prod & 0xffffu);
+}
+
+static std::atomic<int> g_last_cuda_error{0};
 
 }  // namespace hkv
 
-extern "C" int hkv_last_cuda_error(void) { return hkv::g_last_cuda_error; }
+extern "C" int hkv_last_cuda_error(void) { return hkv::g_last_cuda_error.load(std::memory_order_relaxed); }
 
 extern "C" int hkv_version(void) { return 100; }
 
@@ -364,10 +394,24 @@ extern "C" const char* hkv_error_string(int code) {
   }
 }
 
+extern "C" int hkv_selftest_codec(void* out, size_t out_bytes, void* stream) {
+  using namespace hkv;
+  if (!out) return HKV_ERR_NULL;
+  if ((uintptr_t)out & 7) return HKV_ERR_ALIGN;
+  if (out_bytes < HKV_SELFTEST_CODEC_BYTES) return HKV_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemsetAsync(out, 0, 16, st);
+  if (e != cudaSuccess) return record_cuda(e);
+  selftest_e2m1_encode_kernel<<<148 * 8, 256, 0, st>>>((unsigned long long*)out);
+  if ((e = cudaGetLastError()) != cudaSuccess) return record_cuda(e);
+  selftest_decode_table_kernel<<<16, 256, 0, st>>>((uint16_t*)((uint8_t*)out + 16));
+  return record_cuda(cudaGetLastError());
+}
+
 namespace hkv {
 int record_cuda(cudaError_t e) {
   if (e == cudaSuccess) return HKV_OK;
-  g_last_cuda_error = (int)e;
+  g_last_cuda_error.store((int)e, std::memory_order_relaxed);
   return HKV_ERR_CUDA;
 }
 }  // namespace hkv

@@ -80,6 +80,12 @@ def rotate(x: torch.Tensor, signs: torch.Tensor) -> torch.Tensor:
     return (y * scale).view(x.shape)
 
 
+def _check_scales(gk, gv, KVH):
+    for t in (gk, gv):
+        if t.dtype != torch.float32 or t.shape != (KVH,) or not t.is_contiguous():
+            raise TypeError("gk / gv must be contiguous fp32 tensors with one entry per kv head")
+
+
 def _check_signs(signs, D):
     if signs is None:
         return
@@ -96,16 +102,19 @@ def write(key, value, flat, strides, PS, slot_mapping, gk, gv, search=True, sign
     kv_fp4_serving.py:994."""
     if k8 and signs is not None:
         raise ValueError("the K8V4 slot keeps FP8 keys: no rotation")
-    _need_cuda(key, value, slot_mapping, gk, gv, *flat)
-    _check_signs(signs, key.shape[2])
     if key.dtype != torch.bfloat16 or value.dtype != torch.bfloat16:
         raise TypeError("key / value must be bf16")
+    if key.dim() != 3 or value.shape != key.shape:
+        raise ValueError("key / value must be (tokens, kv heads, head_dim) tensors of one shape")
     if key.stride(-1) != 1 or value.stride(-1) != 1:
         raise ValueError("key / value need a contiguous last dimension")
-    if slot_mapping.dtype != torch.int64 or not slot_mapping.is_contiguous():
+    if slot_mapping.dtype != torch.int64 or slot_mapping.dim() != 1 or not slot_mapping.is_contiguous():
         raise TypeError("slot_mapping must be contiguous int64")
     if slot_mapping.shape[0] > key.shape[0]:
         raise ValueError("more slots than tokens")
+    _check_scales(gk, gv, key.shape[1])
+    _need_cuda(key, value, slot_mapping, gk, gv, *flat)
+    _check_signs(signs, key.shape[2])
     KVH, D = key.shape[1], key.shape[2]
     kd, ksf, vd, vsf = flat
     st = (C.c_int64 * 6)(*strides)
@@ -124,29 +133,38 @@ def write(key, value, flat, strides, PS, slot_mapping, gk, gv, search=True, sign
 
 def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_loc, bmm1_scale, bmm2_scale, gk, gv,
                   qlmax, out, workspace, splits=None, nst=None, ncw=None, min_chunk=None, tw=None, signs=None,
-                  k8=False, _combine=True):
+                  k8=False):
     """query (NT, HQ, D) bf16 contiguous; block_tables (B, MP) int32; seq_lens (B,) int32; query_start_loc (B + 1,)
     int32; out (>= NT, HQ, D) bf16, rows of requests without (or with more than qlmax) query tokens are left
     untouched; workspace from alloc_workspace. out = softmax(q k^T * bmm1_scale * gk) v * gv * bmm2_scale.
+    The workspace must have been zero-filled once (alloc_workspace does).
     `splits` bounds the number of stream partitions to B * KVH * splits; the tuning arguments of the reference
     (nst, ncw, min_chunk, tw) are accepted and ignored. signs (D,) fp32 of +-1 on the device: the keys in the cache
     were written rotated, and the kernel rotates the UNROTATED query it is given the same way.
     Signature of kv_fp4_serving.py:894-895."""
     if k8 and signs is not None:
         raise ValueError("the K8V4 slot keeps FP8 keys: no rotation")
-    _need_cuda(query, block_tables, seq_lens, query_start_loc, gk, gv, out, workspace, *flat)
-    _check_signs(signs, query.shape[2])
     if query.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise TypeError("query / out must be bf16")
+    if query.dim() != 3 or out.dim() != 3 or out.shape[1:] != query.shape[1:] or out.shape[0] < query.shape[0]:
+        raise ValueError("query (tokens, heads, head_dim); out (>= tokens, heads, head_dim)")
     if not query.is_contiguous() or not out.is_contiguous():
         raise ValueError("query / out must be contiguous")
     for t in (block_tables, seq_lens, query_start_loc):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise TypeError("block_tables / seq_lens / query_start_loc must be contiguous int32")
+    if block_tables.dim() != 2 or seq_lens.shape != (block_tables.shape[0],) or \
+            query_start_loc.shape != (block_tables.shape[0] + 1,):
+        raise ValueError("block_tables (B, MP); seq_lens (B,); query_start_loc (B + 1,)")
     B, MP = block_tables.shape
     KVH = gk.shape[0]
     HQ, D = query.shape[1], query.shape[2]
+    _check_scales(gk, gv, KVH)
+    if HQ % KVH:
+        raise ValueError("query heads must be a multiple of the kv heads")
     G = HQ // KVH
+    _need_cuda(query, block_tables, seq_lens, query_start_loc, gk, gv, out, workspace, *flat)
+    _check_signs(signs, query.shape[2])
     S = 0 if splits is None else int(splits)
     kd, ksf, vd, vsf = flat
     st = (C.c_int64 * 6)(*strides)
@@ -163,12 +181,7 @@ def decode_ragged(query, flat, strides, PS, block_tables, seq_lens, query_start_
             rc = L.hkv_decode(*args, _ptr(out), s)
         else:
             rc = L.hkv_decode_rot(*args, _ptr(signs), _ptr(out), s)
-        _lib.check(rc, "hkv_decode")
-        if not _combine:                      # (benchmark only: time the decode kernel alone; `out` is incomplete)
-            return out
-        rc = L.hkv_combine(_ptr(workspace), wsb, _ptr(query_start_loc), B, KVH, G, D, int(qlmax), float(bmm2_scale),
-                           _ptr(out), s)
-        _lib.check(rc, "hkv_combine")
+        _lib.check(rc, "hkv_decode")          # (split sequences are merged inside the launch: `out` is complete)
     return out
 
 

@@ -4,13 +4,15 @@ The ops are thin: they pass the tensors' device pointers, the strides and the cu
 (include/hkv.h) and mutate their output arguments in place, like the reference's TileLang-launched kernels mutate the
 cache and the output buffer (kv_fp4_serving.py:994-1005, :894-915 in the reference). Registering them with torch lets
 graph-capturing front ends (torch.compile, vLLM's piecewise graphs) treat the launches as opaque mutating ops. There is
-a CUDA implementation only: calling an op with CPU tensors raises.
+a CUDA implementation only: calling an op with CPU tensors raises. `combine` is kept for the reference's three-launch
+sequence; the merge of split sequences runs inside `decode`, so it launches nothing.
 """
 import ctypes as C
 
 import torch
 
 from . import _lib
+from . import kernels as K
 
 _REGISTERED = False
 
@@ -26,7 +28,7 @@ def _p(t):
 def _strides6(strides):
     if len(strides) != 6:
         raise ValueError("strides must be (data page, data position, data head, scale page, scale position, scale head)")
-    return (C.c_int64 * 6)(*[int(x) for x in strides])
+    return tuple(int(x) for x in strides)
 
 
 def register():
@@ -43,27 +45,23 @@ def register():
     lib.define("combine(Tensor(a!) workspace, Tensor query_start_loc, int num_kv_heads, int group, int head_dim, int qlmax, "
                "float v_scale, Tensor(b!) out) -> ()")
 
+    # the implementations go through the host wrappers of kernels.py, so dtypes, contiguity and shapes are checked
+    # once, in one place, before any pointer reaches the C ABI
     def write(key, value, k_data, k_sf, v_data, v_sf, strides, page_size, slot_mapping, gk, gv, search):
-        with torch.cuda.device(key.device):
-            rc = _lib.load().hkv_write(_p(key), _p(value), key.stride(0), key.stride(1), value.stride(0), value.stride(1),
-                                       _p(k_data), _p(k_sf), _p(v_data), _p(v_sf), _strides6(strides), int(page_size),
-                                       _p(slot_mapping), slot_mapping.shape[0], _p(gk), _p(gv), key.shape[1],
-                                       key.shape[2], int(bool(search)), _stream())
-        _lib.check(rc, "hkv_write")
+        K.write(key, value, (k_data, k_sf, v_data, v_sf), _strides6(strides), int(page_size), slot_mapping, gk, gv,
+                bool(search))
 
     def decode(query, k_data, k_sf, v_data, v_sf, strides, page_size, block_tables, seq_lens, query_start_loc, sm_scale,
                v_scale, gk, gv, qlmax, workspace, splits, out):
-        B, MP = block_tables.shape
-        KVH = gk.shape[0]
-        with torch.cuda.device(query.device):
-            rc = _lib.load().hkv_decode(_p(query), _p(k_data), _p(k_sf), _p(v_data), _p(v_sf), _strides6(strides),
-                                        int(page_size), _p(block_tables), MP, _p(seq_lens), _p(query_start_loc), B, KVH,
-                                        query.shape[1] // KVH, query.shape[2], int(qlmax), float(sm_scale),
-                                        float(v_scale), _p(gk), _p(gv), _p(workspace),
-                                        workspace.numel() * workspace.element_size(), int(splits), _p(out), _stream())
-        _lib.check(rc, "hkv_decode")
+        if block_tables.dim() != 2 or query_start_loc.shape[0] != block_tables.shape[0] + 1 or \
+                seq_lens.shape[0] != block_tables.shape[0]:
+            raise ValueError("block_tables (B, MP), seq_lens (B,), query_start_loc (B + 1,)")
+        K.decode_ragged(query, (k_data, k_sf, v_data, v_sf), _strides6(strides), int(page_size), block_tables, seq_lens,
+                        query_start_loc, float(sm_scale), float(v_scale), gk, gv, int(qlmax), out, workspace,
+                        splits=int(splits) or None)
 
     def combine(workspace, query_start_loc, num_kv_heads, group, head_dim, qlmax, v_scale, out):
+        K._need_cuda(workspace, query_start_loc, out)
         with torch.cuda.device(out.device):
             rc = _lib.load().hkv_combine(_p(workspace), workspace.numel() * workspace.element_size(), _p(query_start_loc),
                                          query_start_loc.shape[0] - 1, int(num_kv_heads), int(group), int(head_dim),

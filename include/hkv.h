@@ -15,6 +15,8 @@
  * synchronises and never reads device data on the host, so a sequence of calls can be captured in a CUDA graph.
  * Host-detectable misuse (null or misaligned pointers, unsupported head_dim / group size / page size, a workspace that
  * is too small) is rejected before anything is launched.
+ * Host threads: the once-per-device set-up that the first decode call on a device performs is serialised internally,
+ * so several host threads may make their first calls at the same time.
  */
 #ifndef HKV_H_
 #define HKV_H_
@@ -57,10 +59,13 @@ int hkv_write(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_
               const float* gk, const float* gv, int KVH, int D, int search, void* stream);
 
 /*
- * Workspace for hkv_decode + hkv_combine on the current device: bytes needed for a batch of up to B requests.
+ * Workspace for hkv_decode on the current device: bytes needed for a batch of up to B requests.
  * The size depends on the device (number of SMs) and on (B, KVH, G, D, qlmax) only, never on context lengths, so one
  * allocation made outside graph capture serves every step. Replaces the sizing loop at backend.py:263-277.
  * Returns 0 for unsupported arguments.
+ * The workspace must be ZERO-FILLED once before its first use (cudaMemsetAsync): it holds the per-sequence ticket
+ * counters of the in-kernel combine, which every launch leaves at zero again. After a launch that reported
+ * HKV_ERR_DEVICE_WAIT the counters are undefined: zero-fill the workspace again before reusing it.
  */
 size_t hkv_decode_workspace_bytes(int B, int KVH, int G, int D, int qlmax);
 
@@ -70,16 +75,17 @@ size_t hkv_decode_workspace_bytes(int B, int KVH, int G, int D, int qlmax);
  *   out[qsl[b] + t, h*G + g, :] = softmax_j(q . k_j * sm_scale * gk[h]) @ v_j * gv[h] * v_scale,  j < L_b - ql_b + t + 1
  * The concatenated (request, kv head) token streams are cut into equal partitions, one per resident CTA; a sequence
  * that lies inside one partition is written to `out` directly, the others leave normalised fp32 partials and
- * log2-sum-exp values in the workspace for hkv_combine. `splits` (1..64, or 0 = automatic) bounds the number of
- * partitions to B * KVH * splits like the reference's grid (kv_fp4_serving.py:889-891); it depends on the batch size
- * only.
+ * log2-sum-exp values in the workspace, and the CTA that finishes a sequence's last outstanding piece merges them in
+ * partition order inside the same launch (the reference's `hz4::combine_rg`, kv_fp4_serving.py:518-558, as a second
+ * launch): `out` is complete when the call's kernels have finished, and the result does not depend on which CTA
+ * merged. `splits` (1..64, or 0 = automatic) bounds the number of partitions to B * KVH * splits like the reference's
+ * grid (kv_fp4_serving.py:889-891); it depends on the batch size only.
  *   q            : bf16 (n_tokens, KVH*G, D) contiguous
  *   block_tables : int32 (B, MP); seq_lens int32 (B); query_start_loc int32 (B + 1)
  *   requests with 0 or more than qlmax query tokens are skipped and their output rows left untouched
  *   out          : bf16 (>= n_tokens, KVH*G, D) contiguous
- * A pass over the cache serves 8 query rows per kv head. G * qlmax <= 8 is one decode launch. Up to 64 rows are
- * accepted: the call then makes ceil(G * qlmax / 8) passes (a decode launch and, for all but the last pass, its
- * combine launch), still followed by one hkv_combine.
+ * A pass over the cache serves 8 query rows per kv head. G * qlmax <= 8 is one launch. Up to 64 rows are accepted:
+ * the call then makes ceil(G * qlmax / 8) launches.
  */
 int hkv_decode(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
                const int64_t strides[6], int PS, const int32_t* block_tables, int MP, const int32_t* seq_lens,
@@ -88,9 +94,9 @@ int hkv_decode(const void* q, const void* kd, const void* ksf, const void* vd, c
                void* stream);
 
 /*
- * Log-sum-exp merge of the partials hkv_decode left in the workspace, in partition order (deterministic).
- * Replaces `hz4::combine_rg` (kv_fp4_serving.py:518-558). Must follow hkv_decode on the same stream with the same
- * (B, KVH, G, D, qlmax, v_scale, out).
+ * Kept for callers written against the reference's three launches (write, decode, combine: `hz4::combine_rg`,
+ * kv_fp4_serving.py:518-558, launched at :913-914). The log-sum-exp merge now runs inside hkv_decode's launch, so this
+ * call checks its arguments and launches nothing.
  */
 int hkv_combine(const void* workspace, size_t workspace_bytes, const int32_t* query_start_loc, int B, int KVH, int G,
                 int D, int qlmax, float v_scale, void* out, void* stream);
@@ -102,7 +108,7 @@ int hkv_combine(const void* workspace, size_t workspace_bytes, const int32_t* qu
  * Who needs it: an inference server usually hands nearly all device memory to one pool at start-up, and a component
  * that is loaded afterwards (a plugin, a sidecar runtime written in another language, code that runs while another
  * library is capturing a CUDA graph) finds cudaMalloc either failing for lack of memory or forbidden outright. Such a
- * caller passes the same inputs and the output buffer as for hkv_decode + hkv_combine, but no workspace: the scratch is
+ * caller passes the same inputs and the output buffer as for hkv_decode, but no workspace: the scratch is
  * a 5 MiB array built into the library (HKV_NOALLOC_SCRATCH_BYTES), resident on every GPU that loads it.
  *
  * Limits and rules:
@@ -113,7 +119,8 @@ int hkv_combine(const void* workspace, size_t workspace_bytes, const int32_t* qu
  *     outside any stream capture.
  *   - All calls on a device share the one array. Two calls whose kernels can overlap on the GPU (different streams
  *     without an ordering between them) race on it; order them on one stream or with events. Nothing in the array has
- *     to be cleared between calls: every call rewrites the part it reads.
+ *     to be cleared between calls: every call rewrites the partials it reads and leaves the ticket counters of the
+ *     in-kernel combine at zero, which is also how the array starts.
  *   - It calls no cudaMalloc / cudaFree and no allocating library routine.
  * Arguments as for hkv_decode (without workspace, workspace_bytes); `out` is complete when the call's kernels finish.
  */
@@ -124,6 +131,13 @@ int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf, const voi
                        float v_scale, const float* gk, const float* gv, int splits, void* out, void* stream);
 
 /*
+ * Status word of the built-in scratch of hkv_decode_noalloc on the current device (HKV_OK or HKV_ERR_DEVICE_WAIT), read
+ * and cleared like hkv_workspace_status does for a caller's workspace; synchronises the stream. No counterpart in the
+ * reference.
+ */
+int hkv_decode_noalloc_status(int* status, void* stream);
+
+/*
  * The same two operations with the reference's optional key rotation (kv_fp4_ref.py:31-35, :55-92): `signs` is a
  * fixed vector of +-1 per channel (fp32[D], 16-byte aligned; the reference's `hadamard_signs`).
  *   hkv_write_rot  quantises k' = FWHT(k * signs) * D^-0.5, computed in fp32 with the reference's butterfly order, from
@@ -131,7 +145,7 @@ int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf, const voi
  *                  (kv_fp4_ref.py:233-241; `hz4::write_task<.., HAD = 1>` kv_fp4_serving.py:621-641).
  *   hkv_decode_rot rotates every query row the same way inside the kernel, rounded once to bf16 like `rotate_q`
  *                  (kv_fp4_ref.py:90-92; the fused rotation of kv_fp4_serving.py:146-189), so q' . k' = q . k and the
- *                  model's math is unchanged. Followed by hkv_combine like hkv_decode.
+ *                  model's math is unchanged.
  * All other arguments as for hkv_write / hkv_decode.
  */
 int hkv_write_rot(const void* key, const void* val, int64_t ks0, int64_t ks1, int64_t vs0, int64_t vs1, void* kd,
@@ -170,7 +184,7 @@ int hkv_dequant(const void* kd, const void* ksf, const void* vd, const void* vsf
  * (page 0, position 0, head 0); strides = {page, position, head} byte strides of kd and vd, then of vsf.
  *   hkv_write_k8   keys e4m3(k / gk[h]) (IEEE division, round to nearest even, saturating at +-448, what vLLM's fp8 cache
  *                  holds), values like hkv_write: byte-exact to `write_reference_k8` (kv_fp4_ref.py:301-311)
- *   hkv_decode_k8  like hkv_decode with key = e4m3 value * gk[h]; followed by hkv_combine. The slots of a head's 16
+ *   hkv_decode_k8  like hkv_decode with key = e4m3 value * gk[h]. The slots of a head's 16
  *                  tokens must be contiguous (dst == 400)
  *   hkv_dequant_k8 like hkv_dequant; keys are the E4M3 values themselves (no gk)
  */
@@ -205,6 +219,21 @@ int hkv_set_option(int option, int value);
  * terminates and the context stays usable; nothing faults.
  */
 int hkv_selftest_wait_timeout(void* workspace, int64_t cycles, void* stream);
+
+/*
+ * Self-test of the narrow-float conversions the kernels stand on, no counterpart in the reference (whose CPU tests
+ * pin the equivalent bit formulas exhaustively: scripts/kernels/kvfp4/test_kvfp4_cpu.py:54-99, :390-434,
+ * test_kvfp4_serving_cpu.py:47-110). Writes to `out` (device memory, 8-byte aligned, HKV_SELFTEST_CODEC_BYTES):
+ *   uint64 [0]  how many of the 2^31 - 2^23 + 1 non-negative fp32 bit patterns 0 .. +inf get a different E2M1 code from
+ *               the hardware conversion the write kernel uses (cvt.rn.satfinite.e2m1x2.f32) than from the reference's
+ *               threshold chain (kv_fp4_ref.py:122-130); must be 0
+ *   uint64 [1]  the same count over the NaN patterns above +inf
+ *   uint16 [16 * 256]  f16 bits of cvt.rn.f16x2.e2m1x2(code) * cvt.rn.f16x2.e4m3x2(scale byte), index code * 256 + byte:
+ *               the dequantised value the decode and dequantisation kernels form
+ * A few milliseconds of GPU time; asynchronous on the stream like every other call.
+ */
+#define HKV_SELFTEST_CODEC_BYTES (16 + 16 * 256 * 2)
+int hkv_selftest_codec(void* out, size_t out_bytes, void* stream);
 
 /*
  * Copies the workspace's device status word to *status (HKV_OK or HKV_ERR_DEVICE_WAIT) and clears it. Synchronises the

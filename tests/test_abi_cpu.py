@@ -103,6 +103,7 @@ def test_dequant_rejects_misuse(lib):
     assert call(start=-1) == -6
     assert call(n=0) == 0
     assert call(ok=C.c_void_p(0x1008)) == -2
+    assert call(start=60, n=8) == -6                           # positions beyond the 4-page block-table row
 
 
 def test_set_option_codes(lib):
@@ -119,3 +120,34 @@ def test_python_wrappers_refuse_cpu_tensors():
     flat = tuple(torch.zeros(16, dtype=torch.uint8) for _ in range(4))
     with pytest.raises(RuntimeError, match="no CPU path"):
         K.write(k, k, flat, (1, 1, 1, 1, 1, 1), 16, torch.zeros(2, dtype=torch.int64), torch.ones(2), torch.ones(2))
+
+
+def test_python_wrappers_check_dtypes_and_shapes_before_any_launch():
+    """a wrong dtype or shape must raise on the host (the C ABI sees raw pointers and could not tell)"""
+    import torch
+    from horizon_kernels_b200 import kernels as K
+    k = torch.zeros(2, 2, 128, dtype=torch.bfloat16)
+    flat = tuple(torch.zeros(16, dtype=torch.uint8) for _ in range(4))
+    st, slots, g = (1, 1, 1, 1, 1, 1), torch.zeros(2, dtype=torch.int64), torch.ones(2)
+    with pytest.raises(TypeError):
+        K.write(k.half(), k, flat, st, 16, slots, g, g)                       # fp16 keys
+    with pytest.raises(TypeError):
+        K.write(k, k, flat, st, 16, slots.int(), g, g)                        # int32 slot ids
+    with pytest.raises(ValueError):
+        K.write(k, k, flat, st, 16, torch.zeros(3, dtype=torch.int64), g, g)  # more slots than tokens
+    with pytest.raises(TypeError):
+        K.write(k, k, flat, st, 16, slots, g.double(), g)                     # fp64 scales
+    q, out, ws = torch.zeros(2, 8, 128, dtype=torch.bfloat16), torch.zeros(2, 8, 128, dtype=torch.bfloat16), flat[0]
+    bt, sl, qsl = torch.zeros(2, 4, dtype=torch.int32), torch.zeros(2, dtype=torch.int32), torch.zeros(3, dtype=torch.int32)
+    with pytest.raises(TypeError):
+        K.decode_ragged(q, flat, st, 16, bt.long(), sl, qsl, 1.0, 1.0, g, g, 1, out, ws)
+    with pytest.raises(ValueError):
+        K.decode_ragged(q, flat, st, 16, bt, sl, qsl[:2], 1.0, 1.0, g, g, 1, out, ws)      # B entries instead of B + 1
+    with pytest.raises(ValueError):
+        K.decode_ragged(q, flat, st, 16, bt, sl, qsl, 1.0, 1.0, g, g, 1, out[:1], ws)      # out shorter than the query
+    with pytest.raises(TypeError):
+        K.decode_ragged(q.float(), flat, st, 16, bt, sl, qsl, 1.0, 1.0, g, g, 1, out, ws)
+    from horizon_kernels_b200 import ops
+    hkv = ops.register()
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        hkv.write(k, k, *flat, list(st), 16, slots, g, g, True)                # CPU tensors: no implementation

@@ -1,0 +1,66 @@
+"""Exhaustive checks of the hardware conversions the kernels stand on, run on the GPU through the C ABI
+(hkv_selftest_codec). The reference pins the equivalent bit formulas of its own kernels exhaustively on the CPU
+(scripts/kernels/kvfp4/test_kvfp4_cpu.py:54-99 and :390-434, test_kvfp4_serving_cpu.py:47-110 in the reference); here
+the formulas are machine instructions, so the check has to run where they execute.
+
+  * write side: cvt.rn.satfinite.e2m1x2.f32 against the reference's threshold chain (kv_fp4_ref.py:122-130) for EVERY
+    non-negative fp32 bit pattern from 0 to +inf;
+  * read side: cvt.rn.f16x2.e2m1x2(code) * cvt.rn.f16x2.e4m3x2(scale byte) in f16 against e2m1_value * e4m3_value for
+    all 16 codes x 256 scale bytes (the product is exact in f16); 0x7f / 0xff are NaN in E4M3 and stay NaN."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from horizon_kernels_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+NBYTES = 16 + 16 * 256 * 2
+
+
+@pytest.fixture(scope="module")
+def selftest():
+    buf = torch.full((NBYTES,), 0xEE, dtype=torch.uint8, device="cuda")
+    rc = _lib.load().hkv_selftest_codec(C.c_void_p(buf.data_ptr()), NBYTES,
+                                        C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    host = buf.cpu().numpy()
+    return host[:16].view(np.uint64), host[16:].view(np.uint16).reshape(16, 256)
+
+
+def test_hardware_e2m1_encode_equals_the_threshold_chain_for_every_non_negative_float(selftest):
+    counts, _ = selftest
+    assert int(counts[0]) == 0          # 0 .. +inf: 2^31 - 2^23 + 1 bit patterns, none differs
+    # NaN inputs: the threshold chain saturates them to code 7 (every comparison is false) and so does the hardware
+    assert int(counts[1]) == 0
+
+
+def test_dequantised_product_table_is_exact(selftest):
+    _, table = selftest
+    got = table.view(np.float16).astype(np.float64)
+    e2m1 = np.array([0, 0.5, 1, 1.5, 2, 3, 4, 6], np.float64)
+    code_val = np.concatenate([e2m1, -e2m1])                              # bit 3 is the sign
+    b = np.arange(256)
+    e, m = (b >> 3) & 15, b & 7
+    mag = np.where(e > 0, (1 + m / 8.0) * 2.0 ** (e - 7), m * 2.0 ** -9)  # e4m3fn: bias 7, subnormals m * 2^-9
+    sc = np.where(b & 0x80, -mag, mag)
+    want = code_val[:, None] * sc[None, :]
+    nan_cols = (b & 0x7F) == 0x7F                                         # 0x7f and 0xff are NaN, there is no infinity
+    assert np.isnan(got[:, nan_cols]).all()
+    ok = ~nan_cols
+    assert np.array_equal(got[:, ok], want[:, ok])
+    # signed zeros: a zero code or a zero scale gives a zero of either sign, never anything else
+    assert (got[0, ok] == 0).all() and (got[:, 0] == 0).all()
+    # the largest product a written cache can hold: code 6 * scale 448
+    assert got[7, 0x7E] == 2688.0
+
+
+def test_selftest_rejects_misuse():
+    L = _lib.load()
+    buf = torch.zeros(NBYTES, dtype=torch.uint8, device="cuda")
+    assert L.hkv_selftest_codec(None, NBYTES, None) == -1
+    assert L.hkv_selftest_codec(C.c_void_p(buf.data_ptr()), NBYTES - 1, None) == -5
+    assert L.hkv_selftest_codec(C.c_void_p(buf.data_ptr() + 4), NBYTES, None) == -2

@@ -1,8 +1,8 @@
 """CPU model of the decode kernel's stream decomposition (horizon_kernels_b200/csrc/hkv_decode.cu): every (request, kv
 head) sequence counts as PIECE_COST cost slots followed by its units; the concatenation is cut into equal partitions;
 a partition's piece of a sequence is the part of the sequence's UNITS inside the partition. The model restates the
-kernel's integer arithmetic (unit count of a partition, piece extents, the slot a partial piece is stored in) and checks
-the invariants the combine kernel relies on."""
+kernel's integer arithmetic (unit count of a partition, piece extents, the slot a partial piece is stored in, the
+ticket counter a split sequence uses) and checks the invariants the in-kernel log-sum-exp merge relies on."""
 import numpy as np
 import pytest
 
@@ -74,8 +74,22 @@ def test_weighted_partitions_cover_every_unit_once_and_keep_the_slot_invariants(
                 else:                                                    # a continuation is the partition's first piece
                     assert i == 0 and first_part < part
     assert len(covered) == sum(Us) * KVH
-    # a split sequence occupies first_part .. last partition without gaps
+    # a split sequence occupies first_part .. last partition without gaps; the closed forms the ticket round uses
+    # (first = u0 // per, last = (u0 + U - 1) // per, pieces = last - first + 1) name exactly those partitions, and no
+    # two split sequences share a ticket counter (the counter's index is the sequence's last partition)
+    Ws = [wt(U, PC) for U in Us]
+    starts = np.concatenate([[0], np.cumsum([W * KVH for W in Ws])])
+    ticket_owner = {}
     for b, U in enumerate(Us):
         for h in range(KVH if U else 0):
             ps = sorted({covered[(b, h, u)] for u in range(U)})
             assert ps == list(range(ps[0], ps[-1] + 1))
+            u0 = int(starts[b]) + h * Ws[b] + PC
+            first, last = u0 // per, (u0 + U - 1) // per
+            assert (first, last) == (ps[0], ps[-1])
+            if first != last:
+                assert last not in ticket_owner
+                ticket_owner[last] = (b, h)
+                # the piece in `last` is that partition's first piece (slot 0), as are those of the partitions between
+                for part in range(first + 1, last + 1):
+                    assert parts[part][0][0][:2] == (b, h)
