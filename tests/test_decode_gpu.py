@@ -172,13 +172,41 @@ def test_error_against_unquantised_fp64_attention():
 
 
 def test_long_context_split_and_combine():
-    """64k tokens on one kv head pair: the sequence is cut over every partition and merged by the combine kernel"""
+    """64k tokens on one kv head pair: the sequence is cut over every partition and merged by the CTA that finishes last"""
     c = build_decode_case(2200, [65536], 2, 8, 128, 16)
     ref = oracle_decode(c)
     out, ws = gpu_decode(c)
     assert K.workspace_status(ws) == 0
     mx, mn, rl = assert_close(out, ref)
     print("64k errors", mx, mn, rl)
+
+
+@pytest.mark.parametrize("D,KVH,G", [(128, 2, 4), (256, 1, 8)])
+def test_every_sequence_split_over_three_or_more_partitions(D, KVH, G):
+    """few long sequences on a grid that fills the GPU: every sequence is cut into many pieces (hundreds of partitions
+    over 2 to 4 sequences), each merged inside the decode launch by whichever CTA finishes its last piece. The result
+    must not depend on which CTA that is: three runs are bit-equal, the ticket counters are back at zero after every
+    launch, and a cap on the partitions (`splits` 1 / 2 / 64, i.e. 1, 2 and up to 64 pieces per sequence) stays within
+    the tolerance."""
+    lens = [9000, 12345]
+    c = build_decode_case(2210 + D, lens, KVH, G, D, 16, ql_list=[1, 2] if G * 2 <= 8 else None)
+    ref = oracle_decode(c, v_scale=0.5)
+    qlmax = 2 if G * 2 <= 8 else 1
+    out, ws = gpu_decode(c, v_scale=0.5, qlmax=qlmax)
+    assert K.workspace_status(ws) == 0
+    assert_close(out, ref)
+    tickets = ws[256:256 + 4 * 2 * K.num_sms()].view(torch.int32)   # the counters of the first 2 * SMs partitions
+    assert int(tickets.abs().sum()) == 0
+    for _ in range(2):
+        o2 = torch.full_like(out, float("nan"))
+        gpu_decode(c, v_scale=0.5, out=o2, ws=ws, qlmax=qlmax)
+        assert torch.equal(o2, out)
+        assert int(tickets.abs().sum()) == 0
+    for splits in (1, 2, 64):
+        o3 = torch.full_like(out, float("nan"))
+        gpu_decode(c, v_scale=0.5, out=o3, ws=ws, splits=splits, qlmax=qlmax)
+        assert_close(o3, ref, f"splits {splits}")
+        assert int(tickets.abs().sum()) == 0
 
 
 def test_graph_replay_with_poisoned_output():
