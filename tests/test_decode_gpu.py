@@ -302,3 +302,32 @@ def test_unsupported_shapes_raise():
     c = build_decode_case(2401, [40], 2, 4, 128, 16, kind="nhd", writer="oracle")
     with pytest.raises(_lib.HkvError, match="unsupported"):
         gpu_decode(c)
+
+
+def test_minimal_workspace_of_a_capped_split_count():
+    """a C caller that caps the partitions with `splits` may pass the smaller workspace that count needs: 1 request x
+    1 kv head x splits 1 = one partition = 8960 bytes at head_dim 128. The call must stay inside it (canary bytes behind
+    it untouched), give the right output, and refuse a workspace one byte shorter."""
+    import ctypes as C
+    c = build_decode_case(2480, [777], 1, 4, 128, 16)
+    cache = c["cache"]
+    dev = cache.phys.device
+    need = 8960                                          # header 256 + tickets 256 + lse 256 + partials 2 * 8 * 128 * 4
+    buf = torch.full((need + 4096,), 0xA5, dtype=torch.uint8, device=dev)
+    buf[:need] = 0
+    q = bf16_tensor(c["q"])
+    out = torch.full(q.shape, float("nan"), dtype=torch.bfloat16, device=dev)
+    bt, sl, qsl = (torch.from_numpy(c[k]).to(dev) for k in ("bt", "seq_lens", "qsl"))
+    gk, gv = torch.from_numpy(c["gk"]).to(dev), torch.from_numpy(c["gv"]).to(dev)
+    st = (C.c_int64 * 6)(*cache.strides)
+    p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+
+    def call(nbytes):
+        return _lib.load().hkv_decode(p(q), *(p(t) for t in cache.flat), st, cache.PS, p(bt), bt.shape[1], p(sl), p(qsl),
+                                      1, 1, 4, 128, 1, c["sm"], 1.0, p(gk), p(gv), p(buf), nbytes, 1, p(out),
+                                      C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert call(need - 1) == -5
+    assert call(need) == 0
+    torch.cuda.synchronize()
+    assert (buf[need:] == 0xA5).all()
+    assert_close(out, oracle_decode(c))
