@@ -224,7 +224,8 @@ def setup_workload(name, device, seed, rank, world, shard=None):
     layer = SimpleNamespace(_k_scale_float=float(gk[0]), _v_scale_float=float(gv[0]), layer_name="layers.0.attn")
     w = SimpleNamespace(name=name, cfg=cfg, NBT=NBT, rows=rows, B=B, pool=pool, flat=flat, strides=strides, gk=gk,
                         gv=gv, batches=batches, impl=impl, builder=builder, layer=layer, device=device,
-                        metas=[builder.build(0, cam_of(bt)) for bt in batches], side=torch.cuda.Stream())
+                        metas=[builder.build(0, cam_of(bt)) for bt in batches], side=torch.cuda.Stream(),
+                        v_scale=float(gv[0]))
 
     def step(i):
         bt, m = w.batches[i % NBT], w.metas[i % NBT]
@@ -243,7 +244,7 @@ def decode_only(w, i):
     bt, m = w.batches[i % w.NBT], w.metas[i % w.NBT]
     v = w.impl._cache_views(w.pool)
     K.decode_ragged(bt.q, v["flat"], v["strides"], w.cfg["PS"], m.block_table, m.seq_lens, m.query_start_loc,
-                    w.impl.scale, float(w.gv[0]), w.gk, w.gv, 1, bt.out, w.impl._state(w.device)["ws"])
+                    w.impl.scale, w.v_scale, w.gk, w.gv, 1, bt.out, w.impl._state(w.device)["ws"])
 
 
 def time_decode_kernel(w, launches, local, seconds=0.35):

@@ -12,16 +12,19 @@ namespace hkv {
 
 // ---------------------------------------------------------------------------------------------------- workspace
 // Layout of the decode workspace (all offsets from the 256-byte aligned base):
-//   Header | tickets[n_parts] int | lse[n_parts][2][RPAD] fp32 | opart[n_parts][2][RPAD][D] fp32
+//   Header | tickets[kMaxParts] int | lse[n_parts][2][RPAD] fp32 | opart[n_parts][2][RPAD][D] fp32
 // Each decode partition (one CTA) owns two partial slots: slot 0 for a sequence piece that begins the partition,
 // slot 1 for a piece that ends it while the sequence continues in the next partition. tickets[p] counts the finished
 // pieces of the split sequence that ENDS in partition p; the CTA that brings it to the number of pieces merges them
-// and sets it back to zero, so the counters are zero between launches (the workspace starts zero-filled).
+// and sets it back to zero, so the counters are zero between launches (the workspace starts zero-filled). The ticket
+// table has a fixed size and place, so that launches with different partition counts on one workspace (another batch
+// size or `splits` cap moves the partial slots) never write partials over a counter.
 struct Header {
   int status;      // HKV_OK or HKV_ERR_DEVICE_WAIT, set by a kernel whose bounded wait ran out
   int pad[15];
 };
 
+constexpr int kMaxParts = 4096;          // partitions (CTAs) of one decode launch: SMs x resident CTAs per SM, capped here
 constexpr int kMaxBatch = 8192;          // requests per decode call (coarse prefix table lives in shared memory)
 constexpr long long kWaitCycles = 1ll << 32;   // bound of every device-side wait, in SM clock cycles (about 2 s)
 
@@ -31,7 +34,7 @@ struct WorkspaceLayout {
   size_t ticket_off, lse_off, opart_off, total;
   __host__ __device__ WorkspaceLayout(int n_parts, int rpad, int D) {
     ticket_off = align_up(sizeof(Header), 256);
-    lse_off = align_up(ticket_off + sizeof(int) * (size_t)n_parts, 256);
+    lse_off = align_up(ticket_off + sizeof(int) * (size_t)kMaxParts, 256);
     opart_off = align_up(lse_off + sizeof(float) * (size_t)n_parts * 2 * rpad, 256);
     total = align_up(opart_off + sizeof(float) * (size_t)n_parts * 2 * rpad * D, 256);
   }

@@ -130,7 +130,7 @@ __device__ __forceinline__ ReqInfo load_req(const DecodeParams& p, int b) {
 
 // a split sequence as the ticket round at the end of a partition needs it
 struct SplitSeq {
-  int b, h, U;                                       // request, kv head, units of the whole sequence
+  int h, U, q0, R;                                   // kv head, units of the whole sequence, first query token, rows of this pass
   long long seq0;                                    // stream position of the sequence (its cost slots come first)
 };
 
@@ -222,7 +222,8 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   int* coarse = reinterpret_cast<int*>(smem + Sm::RING + Sm::BARS + Sm::MERGE);
   __shared__ SplitSeq split[2];
   __shared__ int split_win[2];
-  unsigned pending = 0;                             // bit 0 / 1: the partition's first / last piece belongs to a split sequence
+  unsigned pending = 0, drawn = 0;                  // bit 0 / 1: the partition's first / last piece belongs to a split
+                                                    // sequence; .. and its ticket has been drawn already
 
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g = lane >> 2, c = lane & 3;
   const int KVH = p.KVH, B = p.B;
@@ -234,6 +235,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   float* opart_ws = reinterpret_cast<float*>(p.ws + wl.opart_off);
 
   if (tid < TG * NS) mbar_init(bars + tid, 1);
+  if (tid < 2) split_win[tid] = 0;
   // Every global input may come from the preceding launch, so the kernel waits for it here. The caller may state that
   // the request metadata is older than that launch (hkv_set_option): then the partition search below, which reads only
   // seq_lens and query_start_loc, runs while the preceding launch is still draining, and the wait comes after it.
@@ -476,6 +478,18 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   bool dead = false;                                // a bounded wait ran out: stop consuming
   while (f_n < NS && (int)f_n < n_my) fetch_one(bars_a + 8 * f_n, ring_a + f_n * Gm::STAGE);
 
+  // one thread, after a CTA barrier behind which every thread has fenced its share of the partial: counts this piece
+  // as finished; true when it was the sequence's last outstanding one (then the counter goes back to zero: every piece
+  // has arrived, nobody touches it again in this launch)
+  auto draw_ticket = [&](const SplitSeq& sq) -> int {
+    const long long seq_u0 = sq.seq0 + PC;
+    const int first = (int)(seq_u0 / per), last = (int)((seq_u0 + sq.U - 1) / per);
+    __threadfence();
+    const int win = atomicAdd(tickets + last, 1) == last - first;
+    if (win) tickets[last] = 0;
+    return win;
+  };
+
   // ---- compute side: walk the pieces of the partition
   long long pos = lo;
   int piece_idx = 0, k_units = 0;                   // pieces and units of the partition dealt with so far
@@ -508,9 +522,12 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       // a piece of a split sequence: remember the sequence for the ticket round at the end of the partition (at most
       // two per partition: its first piece and, when the last sequence runs on into the next partition, its last)
       SplitSeq& sq = split[piece_idx == 0 ? 0 : 1];
-      sq.b = b; sq.h = h; sq.U = cw.r.U; sq.seq0 = cw.seq0;
+      sq.h = h; sq.U = cw.r.U; sq.q0 = q0; sq.R = R; sq.seq0 = cw.seq0;
     }
     if (!complete) pending |= piece_idx == 0 ? 1u : 2u;
+    // a split piece that is not the partition's last work draws its ticket as soon as it is stored: the latency passes
+    // behind the SM's other CTAs, and the end of the partition is left with at most one sequence to settle
+    const bool draw_now = !complete && piece_end < hi;
 
     // this warp's units of the piece: blk_first, blk_first + TG, .. < blk_end
     const int blk_first = blk0 + ((w - k0) % TG + TG) % TG, blk_end = blk0 + n_piece;
@@ -874,7 +891,12 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
             *reinterpret_cast<float2*>(dst_p + ch) = make_float2(n0 * inv, n1 * inv);
         }
       }
+      if (draw_now) __threadfence();                 // this thread's part of the partial, visible device-wide
       __syncthreads();
+      if (draw_now) {
+        if (tid == 0) split_win[0] = draw_ticket(split[0]);
+        drawn |= 1u;
+      }
     }
     pos = piece_end;
     ++piece_idx;
@@ -885,22 +907,11 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   // partial was written by many threads: each makes its own writes visible device-wide, the CTA barrier orders them
   // before the thread that draws the ticket, and the merging CTA reads the partials past the L1 (ld.global.cg).
   if (pending) {
-    __threadfence();
+    const unsigned late = pending & ~drawn;          // CTA-uniform: the pieces that ended with the partition
+    if (late) __threadfence();
     __syncthreads();
-    if (tid < 2) {
-      int win = 0;
-      if (pending >> tid & 1u) {
-        const SplitSeq sq = split[tid];
-        const long long seq_u0 = sq.seq0 + PC;
-        const int first = (int)(seq_u0 / per), last = (int)((seq_u0 + sq.U - 1) / per);
-        __threadfence();
-        const int old = atomicAdd(tickets + last, 1);
-        win = old == last - first;
-        if (win) tickets[last] = 0;                  // every piece has arrived: nobody touches the counter again
-      }
-      split_win[tid] = win;
-    }
-    __syncthreads();
+    if (tid < 2 && (late >> tid & 1u)) split_win[tid] = draw_ticket(split[tid]);
+    if (late) __syncthreads();
 #pragma unroll 1
     for (int i = 0; i < 2; ++i) {
       if (!split_win[i]) continue;
@@ -909,9 +920,8 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       const long long seq_u0 = sq.seq0 + PC;
       const int first = (int)(seq_u0 / per), last = (int)((seq_u0 + sq.U - 1) / per);
       const int first_slot = (long long)first * per >= sq.seq0 ? 0 : 1;
-      const ReqInfo r = load_req<LOG_UT>(p, sq.b);
-      merge_split<D>(lse_ws, opart_ws, first, last, first_slot, min(RPAD, p.G * r.ql - p.row0), p.row0, p.G,
-                     p.out + ((long long)r.q0 * (KVH * p.G) + sq.h * p.G) * D, (long long)KVH * p.G * D, p.v_scale);
+      merge_split<D>(lse_ws, opart_ws, first, last, first_slot, sq.R, p.row0, p.G,
+                     p.out + ((long long)sq.q0 * (KVH * p.G) + sq.h * p.G) * D, (long long)KVH * p.G * D, p.v_scale);
     }
   }
 
@@ -971,7 +981,7 @@ static int device_info(DeviceInfo** out) {
 // upper bound of partitions for any layout of this head_dim on this device
 static int max_parts(const DeviceInfo& di, int D) {
   const int i = D == 256;
-  return di.sms * max(1, max(di.ctas_per_sm[i][0], max(di.ctas_per_sm[i][1], di.ctas_per_sm[i][2])));
+  return min(kMaxParts, di.sms * max(1, max(di.ctas_per_sm[i][0], max(di.ctas_per_sm[i][1], di.ctas_per_sm[i][2]))));
 }
 
 }  // namespace hkv
@@ -1031,7 +1041,7 @@ static int decode_impl(const void* q, const void* kd, const void* ksf, const voi
   const int cps = di->ctas_per_sm[D == 256][layout];
   if (cps < 1) return HKV_ERR_UNSUPPORTED;
   (void)max_parts;
-  long long n_parts = (long long)di->sms * cps;
+  long long n_parts = std::min<long long>((long long)di->sms * cps, kMaxParts);
   if (splits > 0) n_parts = std::min<long long>(n_parts, (long long)B * KVH * splits);
   if (n_parts < 1) n_parts = 1;
   if (workspace_bytes < WorkspaceLayout((int)n_parts, RPAD, D).total) return HKV_ERR_WORKSPACE;
@@ -1193,7 +1203,8 @@ extern "C" int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf
   if (rc0 != HKV_OK) return rc0;
   // the scratch a call needs grows with the number of stream partitions, which is bounded by the device's resident
   // CTAs and by B * KVH * splits
-  long long n_parts = (long long)di->sms * std::max(di->ctas_per_sm[D == 256][0], di->ctas_per_sm[D == 256][1]);
+  long long n_parts = std::min<long long>(
+      (long long)di->sms * std::max(di->ctas_per_sm[D == 256][0], di->ctas_per_sm[D == 256][1]), kMaxParts);
   if (splits > 0) n_parts = std::min<long long>(n_parts, (long long)B * KVH * splits);
   if (n_parts < 1) n_parts = 1;
   if (WorkspaceLayout((int)n_parts, RPAD, D).total > kNoAllocScratchBytes) return HKV_ERR_NOALLOC_LIMIT;

@@ -306,13 +306,13 @@ def test_unsupported_shapes_raise():
 
 def test_minimal_workspace_of_a_capped_split_count():
     """a C caller that caps the partitions with `splits` may pass the smaller workspace that count needs: 1 request x
-    1 kv head x splits 1 = one partition = 8960 bytes at head_dim 128. The call must stay inside it (canary bytes behind
+    1 kv head x splits 1 = one partition = 25088 bytes at head_dim 128. The call must stay inside it (canary bytes behind
     it untouched), give the right output, and refuse a workspace one byte shorter."""
     import ctypes as C
     c = build_decode_case(2480, [777], 1, 4, 128, 16)
     cache = c["cache"]
     dev = cache.phys.device
-    need = 8960                                          # header 256 + tickets 256 + lse 256 + partials 2 * 8 * 128 * 4
+    need = 25088                                         # header 256 + tickets 16384 + lse 256 + partials 2 * 8 * 128 * 4
     buf = torch.full((need + 4096,), 0xA5, dtype=torch.uint8, device=dev)
     buf[:need] = 0
     q = bf16_tensor(c["q"])
