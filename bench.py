@@ -539,8 +539,10 @@ def main():
 
     sampler = ClockSampler(local)
     with sampler:
-        # the GPU is kept under the same load before and after the timed steps so that the 20 ms clock samples see it
-        t_end = time.perf_counter() + 0.6
+        # the GPU is kept under the same load before and after the timed steps so that the 20 ms clock samples see it,
+        # and long enough before them for the clocks to settle where the power cap leaves them (they sink for a second
+        # or two after a cold start: timed too early, the steps would look faster than the kernel timed after them)
+        t_end = time.perf_counter() + 2.0
         i = 0
         while time.perf_counter() < t_end:
             graphs[i % NBT].replay()

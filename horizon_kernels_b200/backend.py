@@ -107,14 +107,17 @@ def _build_classes():
 
         @classmethod
         def supported_kv_cache_layouts(cls):
-            # only head-major pages keep a head's 16-token tile contiguous, which the bulk copies need
+            """both page orders of the reference (backend.py:107-110): head-major pages (a head's 16-token tile is one
+            contiguous run, fetched with one bulk copy: the fast path) first, positions-outermost pages second (fetched
+            row by row). The K8V4 slot is served head-major only."""
+            both = _env("HORIZON_KVFP4_K8", "0") != "1"
             try:
                 if _vllm_bases() is None:
                     raise RuntimeError("not inside vLLM")
                 from vllm.v1.kv_cache_interface import KVCacheLayout
-                return (KVCacheLayout.LBHNC,)
+                return (KVCacheLayout.LBHNC, KVCacheLayout.LBNHC) if both else (KVCacheLayout.LBHNC,)
             except Exception:  # noqa: BLE001
-                return ("LBHNC",)
+                return ("LBHNC", "LBNHC") if both else ("LBHNC",)
 
         @classmethod
         def get_supported_head_sizes(cls):

@@ -104,6 +104,18 @@ __device__ __forceinline__ void bulk_g2s_u32(uint32_t dst, const void* src_gmem,
                "l"(src_gmem), "r"(bytes), "r"(bar)
                : "memory");
 }
+// Ampere-style asynchronous copy of N bytes (8 or 16) global -> shared by this thread, and an arrival on an mbarrier that
+// fires when all copies this thread has issued so far have completed (.noinc: the arrival is one of the count the
+// barrier was initialised with)
+template <int N>
+__device__ __forceinline__ void cp_async(uint32_t dst, const void* src) {
+  static_assert(N == 8 || N == 16, "cp.async moves 4, 8 or 16 bytes");
+  if (N == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 // shared-memory loads by 32-bit address. volatile keeps them behind the mbarrier wait that guards the stage.
 __device__ __forceinline__ uint2 lds64(uint32_t a) {
   uint2 r;

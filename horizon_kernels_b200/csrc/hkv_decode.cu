@@ -49,6 +49,7 @@ struct DecodeParams {
   const uint8_t* vd;
   const uint8_t* vsf;
   long long dsh, ssh;                                // byte strides between kv heads (codes, scales)
+  unsigned dst;                                      // byte stride between positions of a page (row-copy layout only)
   unsigned dsp, ssp;                                 // byte strides between pages (codes, scales), < 2^31
   const int* bt;
   const int* seq_lens;
@@ -71,6 +72,10 @@ struct DecodeParams {
 //             outermost inside a page): one bulk copy of 16 * slot bytes per 16 tokens and side
 //   LAYOUT 1  code rows back to back, then the scale rows (the page-region layout of the reference's torch oracle):
 //             two bulk copies per 16 tokens and side
+//   LAYOUT 3  the same token rows as LAYOUT 0, but the rows of a head are NOT back to back in the cache (positions
+//             outermost inside a page, vLLM's NHD order, or any other position / head strides): every lane copies one
+//             row per 16 tokens and side with 8-byte (head_dim 128) or 16-byte (256) cp.async into the stage geometry
+//             of LAYOUT 0, so the compute side is the same
 //   LAYOUT 2  the K8V4 slot (head_dim 256; kv_fp4_ref.py:283-293): token rows of [D signed E4M3 key bytes | D/2 value
 //             codes | D/16 value scales], heads outermost: keys and values of 16 tokens are ONE bulk copy of
 //             16 * 400 bytes; the stage holds those rows as they are
@@ -85,12 +90,14 @@ struct Geo {
   static constexpr int SLOT8 = D + SD + SS;            // K8V4 slot: 400 bytes at head_dim 256
   static constexpr int TILE = UT * SLOT;               // bytes of one (head, side) tile of a unit
   static constexpr int STAGE = K8 ? UT * SLOT8 : 2 * TILE;
-  static constexpr int ROW = K8 ? SLOT8 : LAYOUT == 0 ? SLOT : SD;   // byte stride between token rows in shared memory
+  static constexpr bool SLOTROWS = LAYOUT == 0 || LAYOUT == 3;        // rows of [codes | scales] in shared memory
+  static constexpr bool ROWCOPY = LAYOUT == 3;                         // fetched row by row with cp.async
+  static constexpr int ROW = K8 ? SLOT8 : SLOTROWS ? SLOT : SD;      // byte stride between token rows in shared memory
   static constexpr int SD_ROW = ROW;                   // .. and between the rows of one head in the cache
   static constexpr int KB = K8 ? 16 : 8;               // bytes of one 16-channel key block
   static constexpr int V_BASE = K8 ? D : TILE;         // first value byte of the stage (of row 0)
   static constexpr int SF_BASE = LAYOUT == 1 ? UT * SD : SD;        // value / key scales behind their side's codes
-  static constexpr int SF_ROW = K8 ? SLOT8 : LAYOUT == 0 ? SLOT : SS;
+  static constexpr int SF_ROW = K8 ? SLOT8 : SLOTROWS ? SLOT : SS;
   // What a sequence costs a partition beyond its units (locating it, loading its queries, the end-of-piece merge and
   // the output), in units: measured 3 to 4 microseconds per piece. The stream that is cut into equal partitions counts
   // every sequence as PIECE_COST + its units, so partitions that hold many short sequences get fewer units.
@@ -104,7 +111,7 @@ struct Geo {
   // inside a row) and its value loads (rows i = j, j+2, j+4, j+6, 32 contiguous bytes of each) both touch every
   // shared-memory bank once. 144-byte rows need no permutation.
   __device__ static constexpr int tok(int i) {
-    return (D == 128 && LAYOUT == 0) ? ((i & 5) | ((i & 2) << 2) | ((i & 8) >> 2)) : i;
+    return (D == 128 && SLOTROWS) ? ((i & 5) | ((i & 2) << 2) | ((i & 8) >> 2)) : i;
   }
   // 16-channel block of a key row held by lane column c as its u-th block: NBL adjacent blocks per lane, so that
   // their scale bytes come with one load
@@ -234,7 +241,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   float* lse_ws = reinterpret_cast<float*>(p.ws + wl.lse_off);
   float* opart_ws = reinterpret_cast<float*>(p.ws + wl.opart_off);
 
-  if (tid < TG * NS) mbar_init(bars + tid, 1);
+  if (tid < TG * NS) mbar_init(bars + tid, Gm::ROWCOPY ? 32 : 1);   // (row copies: every lane of the warp arrives)
   if (tid < 2) split_win[tid] = 0;
   // Every global input may come from the preceding launch, so the kernel waits for it here. The caller may state that
   // the request metadata is older than that launch (hkv_set_option): then the partition search below, which reads only
@@ -409,7 +416,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       f_bt = p.bt + (long long)f_b * p.MP;
     }
     if (f_L == 0) {                                 // an empty context has one unit and nothing to read: complete the
-      if (lane == 0) mbar_arrive_u32(bar);          // phase with a plain arrival so that both sides stay in step
+      if (Gm::ROWCOPY || lane == 0) mbar_arrive_u32(bar);   // phase with plain arrivals so that both sides stay in step
       f_fast_end = 0;
       return true;
     }
@@ -432,7 +439,24 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       f_idx += UB;
       const int tok0 = f_blk * UT;
       const int nb = min(UB, (f_L - tok0 + 15) >> 4);          // 16-token blocks of this unit that exist
-      if (elect_one()) {                                        // one lane arms the barrier and issues the copies
+      if (Gm::ROWCOPY) {
+        // lane -> (side, token row) of every 16-token block: SLOT bytes from its own address, in 8- or 16-byte pieces
+        constexpr int CB = D == 128 ? 8 : 16;
+        const int side = lane >> 4, row = lane & 15;
+        const uint8_t* base = side ? f_v : f_k;
+#pragma unroll
+        for (int bi = 0; bi < UB; ++bi) {
+          if (bi < nb) {
+            const unsigned pos0 = (unsigned)(tok0 + 16 * bi) & (unsigned)(p.PS - 1);
+            const uint8_t* src = base + (unsigned long long)(unsigned)page[bi] * p.dsp +
+                                 (unsigned long long)(pos0 + row) * p.dst;
+            const uint32_t dsm = st + bi * (16 * Gm::SLOT) + side * Gm::TILE + row * Gm::SLOT;
+#pragma unroll
+            for (int j = 0; j < Gm::SLOT / CB; ++j) cp_async<CB>(dsm + j * CB, src + j * CB);
+          }
+        }
+        cp_async_mbar_arrive_noinc(bar);                        // arrives once this lane's copies have landed
+      } else if (elect_one()) {                                 // one lane arms the barrier and issues the copies
         mbar_expect_tx_u32(bar, nb * (Gm::STAGE / UB));
 #pragma unroll
         for (int bi = 0; bi < UB; ++bi) {
@@ -940,7 +964,7 @@ int record_cuda(cudaError_t e);
 
 struct DeviceInfo {
   int sms = 0;
-  int ctas_per_sm[2][3] = {{0, 0, 0}, {0, 0, 0}};    // [D == 256][LAYOUT]
+  int ctas_per_sm[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};    // [D == 256][LAYOUT]
   std::atomic<bool> ready{false};                    // set (release) after the fields above, under g_setup_mutex
 };
 static DeviceInfo g_dev[64];
@@ -971,6 +995,8 @@ static int device_info(DeviceInfo** out) {
       if ((e = setup_variant<256, 0>(di.ctas_per_sm[1][0])) != cudaSuccess) return record_cuda(e);
       if ((e = setup_variant<256, 1>(di.ctas_per_sm[1][1])) != cudaSuccess) return record_cuda(e);
       if ((e = setup_variant<256, 2>(di.ctas_per_sm[1][2])) != cudaSuccess) return record_cuda(e);
+      if ((e = setup_variant<128, 3>(di.ctas_per_sm[0][3])) != cudaSuccess) return record_cuda(e);
+      if ((e = setup_variant<256, 3>(di.ctas_per_sm[1][3])) != cudaSuccess) return record_cuda(e);
       di.ready.store(true, std::memory_order_release);
     }
   }
@@ -981,7 +1007,8 @@ static int device_info(DeviceInfo** out) {
 // upper bound of partitions for any layout of this head_dim on this device
 static int max_parts(const DeviceInfo& di, int D) {
   const int i = D == 256;
-  return min(kMaxParts, di.sms * max(1, max(di.ctas_per_sm[i][0], max(di.ctas_per_sm[i][1], di.ctas_per_sm[i][2]))));
+  return min(kMaxParts, di.sms * max(max(1, di.ctas_per_sm[i][3]),
+                                     max(di.ctas_per_sm[i][0], max(di.ctas_per_sm[i][1], di.ctas_per_sm[i][2]))));
 }
 
 }  // namespace hkv
@@ -1028,10 +1055,21 @@ static int decode_impl(const void* q, const void* kd, const void* ksf, const voi
     layout = 0;
   else if (dst == SD && sst == SS)
     layout = 1;
+  else if (sst == dst && dsp == ssp && dsh == ssh && (const uint8_t*)ksf == (const uint8_t*)kd + SD &&
+           (const uint8_t*)vsf == (const uint8_t*)vd + SD)
+    layout = 3;   // rows of [codes | scales] at any position / head strides, e.g. positions outermost inside a page (NHD)
   else
-    return HKV_ERR_UNSUPPORTED;                      // token rows of a head are not contiguous (positions-outer pages)
-  if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kd | (uintptr_t)vd) & 15) return HKV_ERR_ALIGN;
-  if ((dsp | dsh) & 15) return HKV_ERR_ALIGN;
+    return HKV_ERR_UNSUPPORTED;
+  if (((uintptr_t)q | (uintptr_t)out) & 15) return HKV_ERR_ALIGN;
+  if (layout == 3) {
+    // every token row is copied on its own in 8-byte (head_dim 128) or 16-byte (256) pieces
+    const int a = D == 128 ? 7 : 15;
+    if (((uintptr_t)kd | (uintptr_t)vd | (uintptr_t)dsp | (uintptr_t)dst | (uintptr_t)dsh) & a) return HKV_ERR_ALIGN;
+    if (dst < 0 || dst >= (1ll << 31)) return HKV_ERR_RANGE;
+  } else {
+    if (((uintptr_t)kd | (uintptr_t)vd) & 15) return HKV_ERR_ALIGN;
+    if ((dsp | dsh) & 15) return HKV_ERR_ALIGN;
+  }
   if (dsp < 0 || ssp < 0 || dsp >= (1ll << 31) || ssp >= (1ll << 31)) return HKV_ERR_RANGE;   // a page is far below 2 GB
   if (layout == 1 && ((((uintptr_t)ksf | (uintptr_t)vsf) & 15) || ((ssp | ssh) & 15))) return HKV_ERR_ALIGN;
   if ((uintptr_t)workspace & 255) return HKV_ERR_ALIGN;
@@ -1048,7 +1086,7 @@ static int decode_impl(const void* q, const void* kd, const void* ksf, const voi
   DecodeParams p;
   p.q = (const __nv_bfloat16*)q;
   p.kd = (const uint8_t*)kd; p.ksf = (const uint8_t*)ksf; p.vd = (const uint8_t*)vd; p.vsf = (const uint8_t*)vsf;
-  p.dsp = (unsigned)dsp; p.dsh = dsh; p.ssp = (unsigned)ssp; p.ssh = ssh;
+  p.dsp = (unsigned)dsp; p.dsh = dsh; p.ssp = (unsigned)ssp; p.ssh = ssh; p.dst = (unsigned)dst;
   p.bt = block_tables; p.seq_lens = seq_lens; p.qsl = query_start_loc;
   p.gk = gk; p.gv = gv;
   p.ws = (uint8_t*)workspace;
@@ -1064,11 +1102,14 @@ static int decode_impl(const void* q, const void* kd, const void* ksf, const voi
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned grid = (unsigned)n_parts;
   void (*k)(const DecodeParams) =
-      D == 128 ? (layout == 0 ? decode_kernel<128, 0> : decode_kernel<128, 1>)
-               : (layout == 0 ? decode_kernel<256, 0> : layout == 1 ? decode_kernel<256, 1> : decode_kernel<256, 2>);
+      D == 128 ? (layout == 0 ? decode_kernel<128, 0> : layout == 1 ? decode_kernel<128, 1> : decode_kernel<128, 3>)
+               : (layout == 0 ? decode_kernel<256, 0> : layout == 1 ? decode_kernel<256, 1>
+                  : layout == 2 ? decode_kernel<256, 2> : decode_kernel<256, 3>);
   const size_t smem_bytes = D == 128 ? (size_t)Smem<128, 0>::TOTAL
                                      : layout == 2 ? (size_t)Smem<256, 2>::TOTAL : (size_t)Smem<256, 0>::TOTAL;
-  static_assert(Smem<128, 0>::TOTAL == Smem<128, 1>::TOTAL && Smem<256, 0>::TOTAL == Smem<256, 1>::TOTAL, "layouts share a size");
+  static_assert(Smem<128, 0>::TOTAL == Smem<128, 1>::TOTAL && Smem<256, 0>::TOTAL == Smem<256, 1>::TOTAL &&
+                Smem<128, 0>::TOTAL == Smem<128, 3>::TOTAL && Smem<256, 0>::TOTAL == Smem<256, 3>::TOTAL,
+                "layouts share a size");
   // More than RPAD query rows per kv head (large groups, several draft tokens) are served RPAD rows at a time: every
   // pass is one launch over the cache (split sequences are merged inside it).
   for (int row0 = 0; row0 < G * qlmax; row0 += RPAD) {
@@ -1204,7 +1245,7 @@ extern "C" int hkv_decode_noalloc(const void* q, const void* kd, const void* ksf
   // the scratch a call needs grows with the number of stream partitions, which is bounded by the device's resident
   // CTAs and by B * KVH * splits
   long long n_parts = std::min<long long>(
-      (long long)di->sms * std::max(di->ctas_per_sm[D == 256][0], di->ctas_per_sm[D == 256][1]), kMaxParts);
+      (long long)max_parts(*di, D), kMaxParts);
   if (splits > 0) n_parts = std::min<long long>(n_parts, (long long)B * KVH * splits);
   if (n_parts < 1) n_parts = 1;
   if (WorkspaceLayout((int)n_parts, RPAD, D).total > kNoAllocScratchBytes) return HKV_ERR_NOALLOC_LIMIT;

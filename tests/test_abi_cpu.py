@@ -74,7 +74,8 @@ def test_decode_rejects_misuse(lib):
     assert call(B=-1) == -6
     assert call(B=0) == 0
     assert call(B=100000) == -6
-    assert call(st=_strides(18432, 2304, 144, 18432, 2304, 144)) == -3      # positions-outer pages
+    assert call(st=_strides(18432, 2304, 144, 18432, 1152, 144)) == -3      # scales not behind their token's codes
+    assert call(st=_strides(18432, 2300, 144, 18432, 2300, 144)) == -2      # positions-outer rows off the 8-byte grid
     assert call(kd=C.c_void_p(0x1008), ksf=C.c_void_p(0x1008 + 64)) == -2
     assert call(ws=C.c_void_p(0x1010)) == -2
 

@@ -18,8 +18,11 @@ from oracle import kvfp4 as O  # noqa: E402
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("nhd", [False, True])
 @pytest.mark.parametrize("KVH,G,D,PS", [(8, 4, 128, 16), (2, 8, 256, 16), (4, 2, 128, 64)])
-def test_update_then_forward_matches_oracle(KVH, G, D, PS):
+def test_update_then_forward_matches_oracle(KVH, G, D, PS, nhd):
+    """both page orders the backend advertises: head-major (LBHNC) and positions-outermost (LBNHC) physical pages behind
+    the same logical (blocks, 2 * KVH, PS, slot) view"""
     lens = [300, 17, 2049, 64]
     c = synth.paged_case(31 + D + PS, lens, KVH, G, D, PS, outliers=True)
     dev = torch.device("cuda")
@@ -27,17 +30,21 @@ def test_update_then_forward_matches_oracle(KVH, G, D, PS):
     kscale, vscale = 0.04, 0.009
     layer = SimpleNamespace(_k_scale_float=kscale, _v_scale_float=vscale, layer_name="model.layers.3.self_attn.attn")
     impl = BE.HorizonFp4Impl(HQ, D, D ** -0.5, num_kv_heads=KVH, kv_cache_dtype="nvfp4", max_num_seqs=16)
-    kv_cache = Lt.alloc_cache(c["NP"], PS, KVH, D, device=dev, fill=0x7F)
+    if nhd:
+        phys = torch.full((c["NP"], PS, 2 * KVH, Lt.slot_bytes(D)), 0x7F, dtype=torch.uint8, device=dev)
+        kv_cache = phys.permute(0, 2, 1, 3)
+    else:
+        phys = kv_cache = Lt.alloc_cache(c["NP"], PS, KVH, D, device=dev, fill=0x7F)
     # prefill-style write of every cached token as flat (T, KVH * D) tensors, the shape vLLM passes
     key = bf16_tensor(c["key"]).view(-1, KVH * D)
     val = bf16_tensor(c["val"]).view(-1, KVH * D)
     impl.do_kv_cache_update(layer, key, val, kv_cache, torch.from_numpy(c["slots"]).to(dev))
     want = np.full(kv_cache.numel(), 0x7F, np.uint8)
-    lay = O.Layout.slots(PS, KVH, D)
+    lay = O.Layout.slots(PS, KVH, D, nhd=nhd)
     gk = np.full(KVH, kscale, np.float32)
     gv = np.full(KVH, vscale, np.float32)
     O.write(c["key"], c["val"], want, lay, c["slots"], gk, gv, True)
-    assert np.array_equal(kv_cache.cpu().numpy().reshape(-1), want)
+    assert np.array_equal(phys.cpu().numpy().reshape(-1), want)
 
     qsl = torch.from_numpy(c["qsl"])
     cam = SimpleNamespace(num_reqs=B, num_actual_tokens=B, query_start_loc=qsl.to(dev), query_start_loc_cpu=qsl,

@@ -299,9 +299,28 @@ def test_bounded_wait_reports_instead_of_hanging():
 def test_unsupported_shapes_raise():
     with pytest.raises(_lib.HkvError):
         K.alloc_workspace(1, 1, 65, 128, 1)                                # more than 64 query rows per kv head
-    c = build_decode_case(2401, [40], 2, 4, 128, 16, kind="nhd", writer="oracle")
-    with pytest.raises(_lib.HkvError, match="unsupported"):
-        gpu_decode(c)
+    with pytest.raises(_lib.HkvError):
+        K.alloc_workspace(1, 1, 4, 96, 1)                                  # head_dim outside {128, 256}
+
+
+@pytest.mark.parametrize("lens,KVH,G,D,PS", [([40, 1601, 7], 8, 4, 128, 16), ([333, 16, 2048], 3, 4, 128, 32),
+                                             ([129, 300, 70, 5000], 2, 8, 256, 16), ([700, 64], 4, 6, 256, 64)])
+@pytest.mark.parametrize("writer", ["gpu", "oracle"])
+def test_positions_outermost_pages(lens, KVH, G, D, PS, writer):
+    """vLLM's other page order (positions outermost inside a page, NHD: the reference advertises both,
+    backend.py:107-110, and its kernels take any strides, kv_fp4_serving.py:873-886): a head's token rows are not
+    back to back, so the decode copies them row by row. Same numbers as over head-major pages of the same tokens,
+    bit for bit, and within tolerance of the oracle; odd kv head counts put the value rows off the 16-byte grid."""
+    c = build_decode_case(2600 + D + PS, lens, KVH, G, D, PS, kind="nhd", writer=writer)
+    ref = oracle_decode(c, v_scale=0.5)
+    out, ws = gpu_decode(c, v_scale=0.5)
+    assert K.workspace_status(ws) == 0
+    assert_close(out, ref, f"nhd {lens}")
+    c2 = build_decode_case(2600 + D + PS, lens, KVH, G, D, PS, kind="hnd", writer=writer)
+    out2, _ = gpu_decode(c2, v_scale=0.5)
+    assert torch.equal(out, out2)
+    o3, _ = gpu_decode(c, v_scale=0.5, ws=ws, splits=2)
+    assert_close(o3, ref, "splits 2")
 
 
 def test_minimal_workspace_of_a_capped_split_count():
