@@ -67,11 +67,12 @@ struct SplitSeq {
 // w_i = 2^(lse_i - max) / sum, accumulated in partition order with a running maximum, so the result does not depend
 // on which CTA merges. out_row points at row 0 of the (request, kv head) group's first query token; rows of the next
 // token are tok_stride elements further. (Reference: hz4::combine_rg, kv_fp4_serving.py:518-558.)
-template <int D, int RP, int NT>
+// RP: rows of a partial slot in the workspace; NT: threads of the calling group; the call merges rows rbase .. rbase + RB - 1
+template <int D, int RP, int NT, int RB = RP>
 __device__ __forceinline__ void merge_split(const float* lse_ws, const float* opart_ws, int first, int last,
                                             int first_slot, int R, int row0, int G, __nv_bfloat16* out_row,
-                                            long long tok_stride, float v_scale) {
-  constexpr int IT = RP * (D / 2) / NT;      // (row, channel pair) items per thread
+                                            long long tok_stride, float v_scale, int rbase = 0) {
+  constexpr int IT = RB * (D / 2) / NT;      // (row, channel pair) items per thread
   constexpr int GRP = 4;                             // pieces per round: GRP * IT independent loads in flight
   const float ninf = -__int_as_float(0x7f800000);
   float mx[IT], tot[IT], n0[IT], n1[IT];
@@ -82,7 +83,7 @@ __device__ __forceinline__ void merge_split(const float* lse_ws, const float* op
     float2 v[IT][GRP];
 #pragma unroll
     for (int it = 0; it < IT; ++it) {
-      const int idx = threadIdx.x + it * NT, row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
+      const int idx = threadIdx.x + it * NT, row = rbase + idx / (D / 2), ch = (idx - (row - rbase) * (D / 2)) * 2;
 #pragma unroll
       for (int i = 0; i < GRP; ++i) {
         const int pc = pc0 + i;
@@ -115,7 +116,7 @@ __device__ __forceinline__ void merge_split(const float* lse_ws, const float* op
   }
 #pragma unroll
   for (int it = 0; it < IT; ++it) {
-    const int idx = threadIdx.x + it * NT, row = idx / (D / 2), ch = (idx - row * (D / 2)) * 2;
+    const int idx = threadIdx.x + it * NT, row = rbase + idx / (D / 2), ch = (idx - (row - rbase) * (D / 2)) * 2;
     if (row >= R) continue;
     const float inv = tot[it] > 0.0f ? v_scale / tot[it] : 0.0f;
     const int t = (row0 + row) / G, gq = row0 + row - t * G;
