@@ -11,9 +11,9 @@
 The classes derive from vLLM's base classes when vLLM has already been imported by the process (that is, when vLLM
 loads this plugin); otherwise from small stand-ins, so the surface can be exercised and benchmarked without importing
 vLLM. Rows with more query tokens than the decode threshold (prefill over a cached prefix) take the exact
-dequantisation kernel followed by torch's scaled_dot_product_attention per request (a library attention, as the
-reference uses FlashInfer's FA2 there, backend.py:517-543); that path is eager and outside the timed hot path. There is
-no fallback to another backend.
+dequantisation kernel, chunk by chunk, followed by torch matmuls with a running log-sum-exp (library attention, as the
+reference uses FlashInfer's FA2 and merge_state there, backend.py:517-543); that path is eager and outside the timed
+hot path. There is no fallback to another backend.
 """
 import os
 import sys
@@ -225,6 +225,9 @@ def _build_classes():
             self._signs = None
             self.search = _env("HORIZON_KVFP4_SEARCH", "1") == "1"
             self.cps = int(_env("HORIZON_KVFP4_CPS", "0"))        # splits per (request, kv head); 0 = fill the GPU
+            # prefill rows (backend.py:229, :16-25 of the reference): fp16 compute dtype, context chunk in tokens
+            self.pf16 = _env("HORIZON_KVFP4_PF16", "1") == "1"
+            self.prefill_chunk = max(16, int(_env("HORIZON_KVFP4_CHUNK", "65536")))
             self._gk = self._gv = None
             self._views = None
             nspec, max_reqs = 0, int(kwargs.get("max_num_seqs", 0) or 0)
@@ -334,32 +337,58 @@ def _build_classes():
             return output
 
         def _prefill_rows(self, layer, q, v, m, out):
-            """requests with more query tokens than the decode threshold: exact dequantisation of the request's context
-            (the new tokens were written by do_kv_cache_update) to bf16, then attention over it with the causal window
-            of the reference (query token t of ql sees keys j < L - ql + t + 1). The global scales are folded into the
-            softmax scale and the output like the reference's sm / vs (backend.py:517-543). Eager, one request at a
-            time; the mask costs ql * L bytes."""
+            """requests with more query tokens than the decode threshold: the request's context (the new tokens were
+            written by do_kv_cache_update) is dequantised exactly in chunks of HORIZON_KVFP4_CHUNK tokens (65,536, the
+            reference's chunk: backend.py:16-25, :519-543) and attended chunk by chunk with a running log-sum-exp, so
+            the memory held per request is bounded by the chunk, not by the context. Causal window of the reference:
+            query token t of ql sees keys j < L - ql + t + 1. Compute dtype fp16 (HORIZON_KVFP4_PF16=1, the reference's
+            default, backend.py:229: code * scale is exact in fp16) or bf16. The global scales are folded into the
+            softmax scale and the output like the reference's sm / vs. Eager torch matmuls (a library path, as the
+            reference calls FlashInfer there), outside the timed decode path."""
             sm = self.scale * float(layer._k_scale_float)
             vs = float(layer._v_scale_float)
-            KVH, D = self.num_kv_heads, self.head_size
+            KVH, G, D = self.num_kv_heads, self.G, self.head_size
+            dt = torch.float16 if self.pf16 else torch.bfloat16
+            CH = self.prefill_chunk
+            dev = q.device
             for row, q0, q1, L in m.prefill_rows:
                 ql = q1 - q0
                 if ql <= 0 or L <= 0:
                     continue
-                kk = torch.empty((L, KVH, D), dtype=torch.bfloat16, device=q.device)
-                vv = torch.empty_like(kk)
-                K.dequant_tokens(v["flat"], v["strides"], v["PS"], m.block_table[row].contiguous(), 0, L, kk, vv,
-                                 k8=self.k8)
                 qi = q[q0:q1]
                 if self.had:                                                     # the cached keys are rotated
-                    qi = K.rotate(qi, self._rot(q.device)).to(torch.bfloat16)
-                qi = qi.transpose(0, 1).unsqueeze(0)                             # (1, HQ, ql, D)
-                mask = torch.ones((ql, L), dtype=torch.bool, device=q.device).tril_(diagonal=L - ql)
-                o = torch.nn.functional.scaled_dot_product_attention(
-                    qi, kk.transpose(0, 1).unsqueeze(0), vv.transpose(0, 1).unsqueeze(0), attn_mask=mask, scale=sm,
-                    enable_gqa=True)
-                o = o.squeeze(0).transpose(0, 1)                                 # (ql, HQ, D)
-                out[q0:q1].copy_(o * vs if vs != 1.0 else o)
+                    qi = K.rotate(qi, self._rot(dev)).to(torch.bfloat16)
+                # (KVH, G * ql, D): row g * ql + t of a kv head is query head g, token t
+                qh = qi.view(ql, KVH, G, D).permute(1, 2, 0, 3).reshape(KVH, G * ql, D).to(dt)
+                lim = (L - ql + 1 + torch.arange(ql, device=dev)).repeat(G)      # keys visible to every row
+                n_ch = min(CH, L)
+                kk = torch.empty((n_ch, KVH, D), dtype=dt, device=dev)
+                vv = torch.empty_like(kk)
+                # query rows per block so that one block's scores stay near 256 MB
+                QB = max(1, min(G * ql, (256 << 20) // max(1, KVH * n_ch * 4)))
+                acc = torch.zeros((KVH, G * ql, D), dtype=torch.float32, device=dev)
+                mx = torch.full((KVH, G * ql, 1), float("-inf"), dtype=torch.float32, device=dev)
+                den = torch.zeros((KVH, G * ql, 1), dtype=torch.float32, device=dev)
+                bt_row = m.block_table[row].contiguous()
+                for c0 in range(0, L, CH):
+                    n = min(CH, L - c0)
+                    K.dequant_tokens(v["flat"], v["strides"], v["PS"], bt_row, c0, n, kk, vv, k8=self.k8)
+                    kt = kk[:n].permute(1, 2, 0)                                 # (KVH, D, n)
+                    vt = vv[:n].permute(1, 0, 2)                                 # (KVH, n, D)
+                    pos = c0 + torch.arange(n, device=dev)
+                    for r0 in range(0, G * ql, QB):
+                        r1 = min(G * ql, r0 + QB)
+                        s_ = torch.bmm(qh[:, r0:r1], kt).float() * sm            # (KVH, rows, n)
+                        s_.masked_fill_(pos[None, None, :] >= lim[None, r0:r1, None], float("-inf"))
+                        nm = torch.maximum(mx[:, r0:r1], s_.amax(dim=-1, keepdim=True))
+                        nm_safe = torch.where(torch.isinf(nm), torch.zeros_like(nm), nm)
+                        p_ = torch.exp(s_ - nm_safe)
+                        al = torch.exp(mx[:, r0:r1] - nm_safe)
+                        den[:, r0:r1] = den[:, r0:r1] * al + p_.sum(dim=-1, keepdim=True)
+                        acc[:, r0:r1] = acc[:, r0:r1] * al + torch.bmm(p_.to(dt), vt).float()
+                        mx[:, r0:r1] = nm
+                o = acc / den.clamp_min(1e-30) * vs
+                out[q0:q1].copy_(o.view(KVH, G, ql, D).permute(2, 0, 1, 3).reshape(ql, KVH * G, D).to(out.dtype))
 
     return dict(HorizonFp4Backend=HorizonFp4Backend, HorizonFp4Metadata=HorizonFp4Metadata,
                 HorizonFp4Builder=HorizonFp4Builder, HorizonFp4Impl=HorizonFp4Impl)

@@ -62,11 +62,16 @@ def test_update_then_forward_matches_oracle(KVH, G, D, PS, nhd):
     assert (output[B:] == 5.0).all()
 
 
+@pytest.mark.parametrize("chunk,pf16", [("65536", "1"), ("160", "1"), ("96", "0")])
 @pytest.mark.parametrize("KVH,G,D,PS", [(8, 4, 128, 16), (2, 8, 256, 16)])
-def test_mixed_step_with_prefill_rows(KVH, G, D, PS):
+def test_mixed_step_with_prefill_rows(KVH, G, D, PS, chunk, pf16, monkeypatch):
     """a step with decode rows (1 query token) and prefill rows over a cached prefix (37 and 300 query tokens): the
     decode kernel serves the former and leaves the latter untouched, the dequantise + attention path serves the latter;
     both against the oracle with the reference's causal window"""
+    # (prefill contexts are dequantised in chunks merged by a running log-sum-exp: the small chunk sizes cut the 700-token
+    # context into several chunks that do not end on page boundaries; compute dtype fp16 or bf16)
+    monkeypatch.setenv("HORIZON_KVFP4_CHUNK", chunk)
+    monkeypatch.setenv("HORIZON_KVFP4_PF16", pf16)
     lens = [300, 37, 2049, 64, 700]
     qls = [1, 37, 1, 1, 300]
     c = synth.paged_case(77 + D, lens, KVH, G, D, PS, outliers=True, ql_list=qls)
