@@ -374,18 +374,20 @@ def _build_classes():
                     n = min(CH, L - c0)
                     K.dequant_tokens(v["flat"], v["strides"], v["PS"], bt_row, c0, n, kk, vv, k8=self.k8)
                     kt = kk[:n].permute(1, 2, 0)                                 # (KVH, D, n)
-                    vt = vv[:n].permute(1, 0, 2)                                 # (KVH, n, D)
+                    # (KVH, n, D); the value product always takes fp16 operands: the dequantised values are exact in it
+                    # and the probabilities lie in [0, 1]; both products accumulate and return fp32
+                    vt = vv[:n].permute(1, 0, 2).to(torch.float16)
                     pos = c0 + torch.arange(n, device=dev)
                     for r0 in range(0, G * ql, QB):
                         r1 = min(G * ql, r0 + QB)
-                        s_ = torch.bmm(qh[:, r0:r1], kt).float() * sm            # (KVH, rows, n)
+                        s_ = torch.bmm(qh[:, r0:r1], kt, out_dtype=torch.float32) * sm   # (KVH, rows, n), fp32 accumulate and output
                         s_.masked_fill_(pos[None, None, :] >= lim[None, r0:r1, None], float("-inf"))
                         nm = torch.maximum(mx[:, r0:r1], s_.amax(dim=-1, keepdim=True))
                         nm_safe = torch.where(torch.isinf(nm), torch.zeros_like(nm), nm)
                         p_ = torch.exp(s_ - nm_safe)
                         al = torch.exp(mx[:, r0:r1] - nm_safe)
                         den[:, r0:r1] = den[:, r0:r1] * al + p_.sum(dim=-1, keepdim=True)
-                        acc[:, r0:r1] = acc[:, r0:r1] * al + torch.bmm(p_.to(dt), vt).float()
+                        acc[:, r0:r1] = acc[:, r0:r1] * al + torch.bmm(p_.to(torch.float16), vt, out_dtype=torch.float32)
                         mx[:, r0:r1] = nm
                 o = acc / den.clamp_min(1e-30) * vs
                 out[q0:q1].copy_(o.view(KVH, G, ql, D).permute(2, 0, 1, 3).reshape(ql, KVH * G, D).to(out.dtype))

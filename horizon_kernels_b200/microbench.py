@@ -6,7 +6,7 @@ module is what the ncu summaries of the other kernels and variants are captured 
     python -m horizon_kernels_b200.microbench write   [--tokens 32768] [--kvh 8] [--d 128] [--iters 10] [--had] [--k8]
     python -m horizon_kernels_b200.microbench dequant [--tokens 262144] [--kvh 8] [--d 128] [--iters 10] [--f16]
     python -m horizon_kernels_b200.microbench decode  [--batch 192] [--kvh 2] [--g 8] [--d 256] [--min-len 128]
-                                                      [--max-len 32768] [--iters 10] [--had] [--k8]
+                                                      [--max-len 32768] [--iters 10] [--had] [--k8] [--nhd]
 """
 import argparse
 import json
@@ -31,8 +31,13 @@ def _time(fn, iters):
     return e0.elapsed_time(e1) / iters
 
 
-def _pool(NP, KVH, D, PS, k8):
-    """an empty page pool in the FP4 slot layout or the FP8-key slot layout: flat views, strides and the tensor"""
+def _pool(NP, KVH, D, PS, k8, nhd=False):
+    """an empty page pool in the FP4 slot layout (pages head-major, or positions outermost with nhd) or the FP8-key slot
+    layout: flat views, strides and the tensor"""
+    if nhd:
+        pool = torch.zeros((NP, PS, 2 * KVH, Lt.slot_bytes(D)), dtype=torch.uint8, device="cuda")
+        flat, st = Lt.flat_views(*Lt.slot_views(pool.permute(0, 2, 1, 3), KVH, D))
+        return flat, st, pool
     if k8:
         pool = torch.zeros((NP, KVH, PS, Lt.K8_SLOT), dtype=torch.uint8, device="cuda")
         flat, st = Lt.k8_flat_views(*Lt.k8_views(pool, D))
@@ -96,7 +101,7 @@ def decode(a):
     pages = [(n + PS - 1) // PS for n in lens]
     tot, MP = sum(pages), max(pages)
     NP = tot + tot // 4 + 8
-    flat, st, pool = _pool(NP, KVH, D, PS, a.k8)
+    flat, st, pool = _pool(NP, KVH, D, PS, a.k8, a.nhd)
     signs = K.hadamard_signs(D, device="cuda") if a.had else None
     perm = torch.randperm(NP, generator=g, device="cuda")[:tot]
     bt = torch.zeros((B, MP), dtype=torch.int32, device="cuda")
@@ -125,8 +130,8 @@ def decode(a):
     if K.workspace_status(ws) != 0 or not bool(torch.isfinite(out.float()).all()):
         raise RuntimeError("decode reported a wait that ran out, or a non-finite output")
     byts = sum(lens) * KVH * _token_bytes(D, a.k8)
-    print(json.dumps({"kernel": "decode+combine", "batch": B, "kv_heads": KVH, "group": G, "head_dim": D,
-                      "rotated": a.had, "k8": a.k8, "cached_tokens": sum(lens), "cache_mb": byts / 1e6,
+    print(json.dumps({"kernel": "decode", "batch": B, "kv_heads": KVH, "group": G, "head_dim": D,
+                      "rotated": a.had, "k8": a.k8, "positions_outermost_pages": a.nhd, "cached_tokens": sum(lens), "cache_mb": byts / 1e6,
                       "us": ms * 1e3, "algorithmic_gbs": byts / ms / 1e6}))
 
 
@@ -142,6 +147,7 @@ def main():
     ap.add_argument("--max-len", type=int, default=32768)
     ap.add_argument("--had", action="store_true", help="rotated keys (sign flips + Hadamard transform)")
     ap.add_argument("--k8", action="store_true", help="the FP8-key slot (head_dim 256)")
+    ap.add_argument("--nhd", action="store_true", help="decode: pages with positions outermost (row-copy path)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--f16", action="store_true")
     a = ap.parse_args()
