@@ -10,7 +10,7 @@ EXPORTS = ("hkv_version", "hkv_error_string", "hkv_last_cuda_error", "hkv_write"
            "hkv_decode", "hkv_combine", "hkv_workspace_status", "hkv_decode_noalloc", "hkv_decode_noalloc_status",
            "hkv_set_option", "hkv_dequant", "hkv_write_rot",
            "hkv_decode_rot", "hkv_write_k8", "hkv_decode_k8", "hkv_dequant_k8",
-           "hkv_selftest_wait_timeout", "hkv_selftest_codec")
+           "hkv_selftest_wait_timeout", "hkv_selftest_codec", "hkv_probe_issue_rates")
 
 _lib = None
 
@@ -72,6 +72,8 @@ def load():
         L.hkv_selftest_wait_timeout.argtypes = [vp, i64, vp]
         L.hkv_selftest_codec.restype = i32
         L.hkv_selftest_codec.argtypes = [vp, C.c_size_t, vp]
+        L.hkv_probe_issue_rates.restype = i32
+        L.hkv_probe_issue_rates.argtypes = [vp, C.c_size_t, i32, vp]
         L.hkv_set_option.restype = i32
         L.hkv_set_option.argtypes = [i32, i32]
         L.hkv_workspace_status.restype = i32

@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(OUT_DIR, "libhkv.so")
-SOURCES = ["hkv_write.cu", "hkv_decode.cu", "hkv_dequant.cu"]
+SOURCES = ["hkv_write.cu", "hkv_decode.cu", "hkv_dequant.cu", "hkv_probe.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-shared", "-cudart", "static"]
 

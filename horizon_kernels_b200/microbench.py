@@ -5,6 +5,7 @@ module is what the ncu summaries of the other kernels and variants are captured 
 
     python -m horizon_kernels_b200.microbench write   [--tokens 32768] [--kvh 8] [--d 128] [--iters 10] [--had] [--k8]
     python -m horizon_kernels_b200.microbench dequant [--tokens 262144] [--kvh 8] [--d 128] [--iters 10] [--f16]
+    python -m horizon_kernels_b200.microbench pipes
     python -m horizon_kernels_b200.microbench decode  [--batch 192] [--kvh 2] [--g 8] [--d 256] [--min-len 128]
                                                       [--max-len 32768] [--iters 10] [--had] [--k8] [--nhd]
 """
@@ -135,9 +136,30 @@ def decode(a):
                       "us": ms * 1e3, "algorithmic_gbs": byts / ms / 1e6}))
 
 
+def pipes(a):
+    """cycles per warp instruction and SM sub-partition for the instruction kinds of the decode kernel
+    (hkv_probe_issue_rates in include/hkv.h), at 1, 3 and 4 warps per sub-partition"""
+    import ctypes as C
+    from . import _lib
+    names = ["cvt.rn.f16x2.e2m1x2", "mul.f16x2", "fma.f32", "lop3", "4 cvt + 4 mul.f16x2", "4 cvt + 4 mul + 1 add",
+             "4 cvt + 4 mul + 1 add + mma.m16n8k16"]
+    per_rep = [8, 8, 8, 8, 8, 9, 10]
+    nbytes = 7 * 256 * 8 + 256 * 1024 * 4
+    buf = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for wps in (1, 3, 4):
+        _lib.check(_lib.load().hkv_probe_issue_rates(C.c_void_p(buf.data_ptr()), nbytes, wps,
+                                                     C.c_void_p(torch.cuda.current_stream().cuda_stream)), "hkv_probe_issue_rates")
+        torch.cuda.synchronize()
+        cyc = buf[:7 * 256 * 8].view(torch.int64).view(7, 256)[:, :sms].double().mean(dim=1).cpu().tolist()
+        print(json.dumps({"kernel": "pipes", "warps_per_subpartition": wps, "cycles_per_warp_instruction": {
+            n: round(c / (2048 * k * wps), 3) for n, c, k in zip(names, cyc, per_rep)},
+            "cycles_per_repetition": {n: round(c / (2048 * wps), 2) for n, c in zip(names[4:], cyc[4:])}}))
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["write", "dequant", "decode"])
+    ap.add_argument("kernel", choices=["write", "dequant", "decode", "pipes"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--kvh", type=int, default=None)
     ap.add_argument("--d", type=int, default=None, choices=[128, 256])
@@ -157,7 +179,7 @@ def main():
         a.kvh = 2 if a.kernel == "decode" else 8
     if a.d is None:
         a.d = 256 if (a.kernel == "decode" or a.k8) else 128
-    {"write": write, "dequant": dequant, "decode": decode}[a.kernel](a)
+    {"write": write, "dequant": dequant, "decode": decode, "pipes": pipes}[a.kernel](a)
 
 
 if __name__ == "__main__":

@@ -236,6 +236,20 @@ int hkv_selftest_wait_timeout(void* workspace, int64_t cycles, void* stream);
 int hkv_selftest_codec(void* out, size_t out_bytes, void* stream);
 
 /*
+ * Issue-rate probe, no counterpart in the reference: times, with the SM clock counter, unrolled sequences of the
+ * instruction kinds the decode kernel is made of, `warps_per_subpartition` (1..8) warps per SM sub-partition, one block
+ * per SM. Results in `scratch` (device memory, 8-byte aligned, HKV_PROBE_SCRATCH_BYTES): int64 cycles[7][256], entry
+ * [mode][sm] = cycles that SM's block took for 2048 repetitions per warp of
+ *   mode 0: 8 cvt.rn.f16x2.e2m1x2   1: 8 mul.f16x2   2: 8 fma.f32   3: 8 lop3   4: 4 conversions + 4 multiplies
+ *   mode 5: 4 conversions + 4 multiplies + 1 integer add (the decode kernel's dequantise group without its mma)
+ *   mode 6: mode 5 + one mma.sync.m16n8k16 (10 instructions per repetition)
+ * cycles / (2048 * instructions per repetition * warps_per_subpartition) = cycles per warp instruction and
+ * sub-partition. `python -m horizon_kernels_b200.microbench pipes` prints them. Asynchronous on the stream.
+ */
+#define HKV_PROBE_SCRATCH_BYTES (7 * 256 * 8 + 256 * 1024 * 4)
+int hkv_probe_issue_rates(void* scratch, size_t scratch_bytes, int warps_per_subpartition, void* stream);
+
+/*
  * Copies the workspace's device status word to *status (HKV_OK or HKV_ERR_DEVICE_WAIT) and clears it. Synchronises the
  * stream: a debugging aid, not for the hot path.
  */
