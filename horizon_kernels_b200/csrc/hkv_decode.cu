@@ -90,28 +90,31 @@ struct Geo {
   __device__ static constexpr int kblk(int c, int u) { return NBL * c + u; }
 };
 
-template <int D, int LAYOUT>
+// QT: 8-row query tiles of one pass (1, or 2 at head_dim 128: sixteen query rows per kv head read the cache once)
+template <int D, int LAYOUT, int QT = 1>
 struct Smem {
   using G_ = Geo<D, LAYOUT>;
+  static constexpr int RP = RPAD * QT;                              // query rows of one pass
   static constexpr int RING = TG * G_::NS * G_::STAGE;
   static constexpr int BARS = TG * G_::NS * 8;
   static constexpr int OROW = D + 4;                               // padded accumulator row (floats)
-  static constexpr int MERGE = TG * RPAD * OROW * 4 + TG * RPAD * 2 * 4;
+  static constexpr int MERGE = TG * RP * OROW * 4 + TG * RP * 2 * 4;
   static constexpr int COARSE = (kMaxBatch / 32 + 2) * 4;
   static constexpr int TOTAL = RING + BARS + MERGE + COARSE + 64;
 };
 
-template <int D, int LAYOUT>
-__global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(const DecodeParams p) {
+template <int D, int LAYOUT, int QT = 1>
+__global__ void __launch_bounds__(NTHREADS, QT == 2 ? 2 : Geo<D, LAYOUT>::MINB) decode_kernel(const DecodeParams p) {
   using Gm = Geo<D, LAYOUT>;
-  using Sm = Smem<D, LAYOUT>;
+  using Sm = Smem<D, LAYOUT, QT>;
+  constexpr int RP = Sm::RP;
   constexpr int NS = Gm::NS, UB = Gm::UB, UT = Gm::UT, LOG_UT = Gm::LOG_UT;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Sm::RING);
   float* obuf = reinterpret_cast<float*>(smem + Sm::RING + Sm::BARS);
-  float* mbuf = obuf + TG * RPAD * Sm::OROW;
-  float* lbuf = mbuf + TG * RPAD;
+  float* mbuf = obuf + TG * RP * Sm::OROW;
+  float* lbuf = mbuf + TG * RP;
   int* coarse = reinterpret_cast<int*>(smem + Sm::RING + Sm::BARS + Sm::MERGE);
   __shared__ SplitSeq split[2];
   __shared__ int split_win[2];
@@ -122,7 +125,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
   const int KVH = p.KVH, B = p.B;
   Header* hdr = reinterpret_cast<Header*>(p.ws);
   const int n_parts = gridDim.x, part = blockIdx.x;
-  const WorkspaceLayout wl(n_parts, RPAD, D);
+  const WorkspaceLayout wl(n_parts, RP, D);
   int* tickets = reinterpret_cast<int*>(p.ws + wl.ticket_off);
   float* lse_ws = reinterpret_cast<float*>(p.ws + wl.lse_off);
   float* opart_ws = reinterpret_cast<float*>(p.ws + wl.opart_off);
@@ -417,7 +420,7 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
     const int k0 = k_units;                         // partition-local index of the piece's first unit
     k_units += n_piece;
     const int b = cw.b, h = cw.h, L = cw.r.L, ql = cw.r.ql, q0 = cw.r.q0, G = p.G;
-    const int R = min(RPAD, G * ql - p.row0);      // query rows of this pass: rows row0 .. row0 + R - 1 of the group
+    const int R = min(RP, G * ql - p.row0);      // query rows of this pass: rows row0 .. row0 + R - 1 of the group
     const bool complete = blk0 == 0 && piece_end == seq_end;
     if (kQueryPrefetch && w == 0 && piece_end < hi) {
       // the partition goes on with the next sequence: ask for its query rows now (L2 prefetch, no registers held), so
@@ -442,10 +445,16 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
     // this warp's units of the piece: blk_first, blk_first + TG, .. < blk_end
     const int blk_first = blk0 + ((w - k0) % TG + TG) % TG, blk_end = blk0 + n_piece;
     // running max (raw score units) and sum of query rows 2c and 2c+1 over this lane's tokens
-    float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;
-    float o[Gm::KS][4];
+    // (per 8-row query tile q: rows 8 q + 2c and 8 q + 2c + 1)
+    float m0[QT], m1[QT], l0[QT], l1[QT];
+    float o[QT][Gm::KS][4];
 #pragma unroll
-    for (int j = 0; j < Gm::KS; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+    for (int q = 0; q < QT; ++q) {
+      m0[q] = m1[q] = NEG_BIG;
+      l0[q] = l1[q] = 0.0f;
+#pragma unroll
+      for (int j = 0; j < Gm::KS; ++j) o[q][j][0] = o[q][j][1] = o[q][j][2] = o[q][j][3] = 0.0f;
+    }
 
     if (blk_first < blk_end && !dead) {
       // softmax scale in the log2 domain. A negative scale is moved into the query so that "max" stays a max.
@@ -454,10 +463,11 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       sc = fmaxf(fabsf(sc), 1e-30f);
       const float tau_raw = TAU / sc;
       // query fragments: row g of the (request, kv head) group, channels of this lane's key blocks, as f16
-      uint32_t qa[Gm::KS][2];
-      {
-        const bool have = g < R;
-        const int t = have ? (p.row0 + g) / G : 0, gq = have ? p.row0 + g - t * G : 0;
+      uint32_t qa[QT][Gm::KS][2];
+#pragma unroll
+      for (int q = 0; q < QT; ++q) {
+        const bool have = g + 8 * q < R;
+        const int t = have ? (p.row0 + g + 8 * q) / G : 0, gq = have ? p.row0 + g + 8 * q - t * G : 0;
         const __nv_bfloat16* qrow = p.q + ((long long)(q0 + t) * (KVH * G) + h * G + gq) * D;
         constexpr int NQ = 16 * Gm::NBL;            // this lane's channels: NQ * c .. NQ * c + NQ - 1 of the row
         float qf[NQ];
@@ -513,15 +523,24 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
         for (int i = 0; i < NQ / 2; ++i) {
           float a = qf[2 * i], bq = qf[2 * i + 1];
           if (flip) { a = -a; bq = -bq; }
-          qa[i >> 1][i & 1] = pack_f16x2_sat(a, bq);   // values beyond f16's range become +-65504
+          qa[q][i >> 1][i & 1] = pack_f16x2_sat(a, bq);   // values beyond f16's range become +-65504
         }
       }
       // visible context of query rows 2c, 2c+1 (causal among the request's own query tokens)
-      const int lim0 = 2 * c < R ? L - ql + (p.row0 + 2 * c) / G + 1 : L,
-                lim1 = 2 * c + 1 < R ? L - ql + (p.row0 + 2 * c + 1) / G + 1 : L;
+      int lim0[QT], lim1[QT];
+#pragma unroll
+      for (int q = 0; q < QT; ++q) {
+        const int ra = 8 * q + 2 * c, rb = ra + 1;
+        lim0[q] = ra < R ? L - ql + (p.row0 + ra) / G + 1 : L;
+        lim1[q] = rb < R ? L - ql + (p.row0 + rb) / G + 1 : L;
+      }
       const int blk_mask = (L - ql + p.row0 / G + 1) >> LOG_UT;   // units below this one are visible to every row in full
-      float mneg0 = -m0 * sc, mneg1 = -m1 * sc;      // p = 2^(s * sc + mneg)
-      float thr0 = m0 + tau_raw, thr1 = m1 + tau_raw;
+      float mneg0[QT], mneg1[QT], thr0[QT], thr1[QT];   // p = 2^(s * sc + mneg)
+#pragma unroll
+      for (int q = 0; q < QT; ++q) {
+        mneg0[q] = -m0[q] * sc; mneg1[q] = -m1[q] * sc;
+        thr0[q] = m0[q] + tau_raw; thr1[q] = m1[q] + tau_raw;
+      }
 
       // waits (bounded) for the next stage this warp consumes; false once a wait ran out
       // (the stage's addresses come back in bar and st: the unit fetched after it reuses them)
@@ -540,13 +559,15 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       };
 
       // ---------------- S^T = K Q^T per 16-token block: rows = tokens, columns = query rows
-      auto k_phase = [&](const uint32_t st, float (&x)[UB][4]) {
+      auto k_phase = [&](const uint32_t st, float (&x)[QT][UB][4]) {
         const uint32_t kd_ = st + koff_d, ks_ = st + koff_s;
 #pragma unroll
         for (int bi = 0; bi < UB; ++bi) {
-          float sa[Gm::NCH][4];
+          float sa[QT][Gm::NCH][4];
 #pragma unroll
-          for (int i = 0; i < Gm::NCH; ++i) sa[i][0] = sa[i][1] = sa[i][2] = sa[i][3] = 0.0f;
+          for (int q = 0; q < QT; ++q)
+#pragma unroll
+            for (int i = 0; i < Gm::NCH; ++i) sa[q][i][0] = sa[q][i][1] = sa[q][i][2] = sa[q][i][3] = 0.0f;
           if (Gm::K8) {
             // FP8 keys: 16 bytes per block and row, no block scale (the global scale is part of `sc`)
             const int dk8 = bi * 16 * Gm::ROW;
@@ -559,11 +580,15 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
                 uint32_t a0, a2, a1, a3;
                 e4m3x4_to_f16x2(wa[v], a0, a2);
                 e4m3x4_to_f16x2(wb[v], a1, a3);
-                mma_f16(sa[v & (Gm::NCH - 1)], a0, a1, a2, a3, qa[4 * u + v][0], qa[4 * u + v][1]);
+#pragma unroll
+                for (int q = 0; q < QT; ++q)
+                  mma_f16(sa[q][v & (Gm::NCH - 1)], a0, a1, a2, a3, qa[q][4 * u + v][0], qa[q][4 * u + v][1]);
               }
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) x[bi][i] = Gm::NCH == 2 ? sa[0][i] + sa[Gm::NCH - 1][i] : sa[0][i];
+            for (int q = 0; q < QT; ++q)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) x[q][bi][i] = Gm::NCH == 2 ? sa[q][0][i] + sa[q][Gm::NCH - 1][i] : sa[q][0][i];
             continue;
           }
           // codes and scales of this lane's NBL adjacent key blocks of rows r0 and r1
@@ -600,24 +625,30 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
             e2m1x8_to_f16x2(w1[u].x, e2);
             e2m1x8_to_f16x2(w1[u].y, e3);
             // k-step v of this block: A = {row r0 k-low, row r1 k-low, row r0 k-high, row r1 k-high}
-            mma_f16(sa[0], hmul2h(e0[0], sf0), hmul2h(e2[0], sf1), hmul2h(e0[1], sf0), hmul2h(e2[1], sf1),
-                    qa[4 * u + 0][0], qa[4 * u + 0][1]);
-            mma_f16(sa[Gm::NCH - 1], hmul2h(e0[2], sf0), hmul2h(e2[2], sf1), hmul2h(e0[3], sf0), hmul2h(e2[3], sf1),
-                    qa[4 * u + 1][0], qa[4 * u + 1][1]);
-            mma_f16(sa[0], hmul2h(e1[0], sf0), hmul2h(e3[0], sf1), hmul2h(e1[1], sf0), hmul2h(e3[1], sf1),
-                    qa[4 * u + 2][0], qa[4 * u + 2][1]);
-            mma_f16(sa[Gm::NCH - 1], hmul2h(e1[2], sf0), hmul2h(e3[2], sf1), hmul2h(e1[3], sf0), hmul2h(e3[3], sf1),
-                    qa[4 * u + 3][0], qa[4 * u + 3][1]);
+            // (the dequantised A fragments serve every query tile)
+            const uint32_t A0[4] = {hmul2h(e0[0], sf0), hmul2h(e2[0], sf1), hmul2h(e0[1], sf0), hmul2h(e2[1], sf1)};
+            const uint32_t A1[4] = {hmul2h(e0[2], sf0), hmul2h(e2[2], sf1), hmul2h(e0[3], sf0), hmul2h(e2[3], sf1)};
+            const uint32_t A2[4] = {hmul2h(e1[0], sf0), hmul2h(e3[0], sf1), hmul2h(e1[1], sf0), hmul2h(e3[1], sf1)};
+            const uint32_t A3[4] = {hmul2h(e1[2], sf0), hmul2h(e3[2], sf1), hmul2h(e1[3], sf0), hmul2h(e3[3], sf1)};
+#pragma unroll
+            for (int q = 0; q < QT; ++q) {
+              mma_f16(sa[q][0], A0[0], A0[1], A0[2], A0[3], qa[q][4 * u + 0][0], qa[q][4 * u + 0][1]);
+              mma_f16(sa[q][Gm::NCH - 1], A1[0], A1[1], A1[2], A1[3], qa[q][4 * u + 1][0], qa[q][4 * u + 1][1]);
+              mma_f16(sa[q][0], A2[0], A2[1], A2[2], A2[3], qa[q][4 * u + 2][0], qa[q][4 * u + 2][1]);
+              mma_f16(sa[q][Gm::NCH - 1], A3[0], A3[1], A3[2], A3[3], qa[q][4 * u + 3][0], qa[q][4 * u + 3][1]);
+            }
           }
 #pragma unroll
-          for (int i = 0; i < 4; ++i) x[bi][i] = Gm::NCH == 2 ? sa[0][i] + sa[Gm::NCH - 1][i] : sa[0][i];
+          for (int q = 0; q < QT; ++q)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x[q][bi][i] = Gm::NCH == 2 ? sa[q][0][i] + sa[q][Gm::NCH - 1][i] : sa[q][0][i];
         }
       };
 
       // ---------------- online softmax (raw score units): this lane holds query rows 2c, 2c+1 of tokens r0, r1 of
       // every block; x[bi] = {(r0, row 2c), (r0, row 2c+1), (r1, row 2c), (r1, row 2c+1)}. Leaves P^T as the B
       // operand of the second product in pb.
-      auto softmax = [&](const uint32_t st, const int blk, float (&x)[UB][4], uint32_t (&pb)[UB][2]) {
+      auto softmax = [&](const uint32_t st, const int blk, float (&x)[QT][UB][4], uint32_t (&pb)[QT][UB][2]) {
         const int tbase = blk * UT;
         if (blk >= blk_mask) {                        // warp-uniform: only the last unit(s) of a sequence
           // rows past the context hold arbitrary bytes: their scores become -inf below, and their value scales are
@@ -631,53 +662,67 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
           __syncwarp();
           const float ninf = -__int_as_float(0x7f800000);
 #pragma unroll
-          for (int bi = 0; bi < UB; ++bi) {
-            const int ta = tbase + 16 * bi + r0, tb = tbase + 16 * bi + r1;
-            x[bi][0] = ta < lim0 ? x[bi][0] : ninf;
-            x[bi][1] = ta < lim1 ? x[bi][1] : ninf;
-            x[bi][2] = tb < lim0 ? x[bi][2] : ninf;
-            x[bi][3] = tb < lim1 ? x[bi][3] : ninf;
-          }
+          for (int q = 0; q < QT; ++q)
+#pragma unroll
+            for (int bi = 0; bi < UB; ++bi) {
+              const int ta = tbase + 16 * bi + r0, tb = tbase + 16 * bi + r1;
+              x[q][bi][0] = ta < lim0[q] ? x[q][bi][0] : ninf;
+              x[q][bi][1] = ta < lim1[q] ? x[q][bi][1] : ninf;
+              x[q][bi][2] = tb < lim0[q] ? x[q][bi][2] : ninf;
+              x[q][bi][3] = tb < lim1[q] ? x[q][bi][3] : ninf;
+            }
         }
         // the running max moves only when some score exceeds it by more than TAU (then P stays below 2^TAU, inside
         // f16); the cross-lane maximum is needed only in that case
-        float bm0 = fmaxf(x[0][0], x[0][2]), bm1 = fmaxf(x[0][1], x[0][3]);
+        float bm0[QT], bm1[QT];
+        bool over = false;
 #pragma unroll
-        for (int bi = 1; bi < UB; ++bi) {
-          bm0 = fmaxf(bm0, fmaxf(x[bi][0], x[bi][2]));
-          bm1 = fmaxf(bm1, fmaxf(x[bi][1], x[bi][3]));
-        }
-        if (__any_sync(0xffffffffu, (bm0 > thr0) | (bm1 > thr1))) {
+        for (int q = 0; q < QT; ++q) {
+          bm0[q] = fmaxf(x[q][0][0], x[q][0][2]);
+          bm1[q] = fmaxf(x[q][0][1], x[q][0][3]);
 #pragma unroll
-          for (int of = 4; of < 32; of <<= 1) {
-            bm0 = fmaxf(bm0, __shfl_xor_sync(0xffffffffu, bm0, of));
-            bm1 = fmaxf(bm1, __shfl_xor_sync(0xffffffffu, bm1, of));
+          for (int bi = 1; bi < UB; ++bi) {
+            bm0[q] = fmaxf(bm0[q], fmaxf(x[q][bi][0], x[q][bi][2]));
+            bm1[q] = fmaxf(bm1[q], fmaxf(x[q][bi][1], x[q][bi][3]));
           }
-          const float n0 = fmaxf(m0, fmaxf(bm0, NEG_BIG)), n1 = fmaxf(m1, fmaxf(bm1, NEG_BIG));
-          const float al0 = fast_exp2((m0 - n0) * sc), al1 = fast_exp2((m1 - n1) * sc);
-          m0 = n0; m1 = n1;
-          mneg0 = -n0 * sc; mneg1 = -n1 * sc;
-          thr0 = n0 + tau_raw; thr1 = n1 + tau_raw;
-          l0 *= al0; l1 *= al1;
+          over |= (bm0[q] > thr0[q]) | (bm1[q] > thr1[q]);
+        }
+        if (__any_sync(0xffffffffu, over)) {
 #pragma unroll
-          for (int j = 0; j < Gm::KS; ++j) {
-            o[j][0] *= al0; o[j][1] *= al1; o[j][2] *= al0; o[j][3] *= al1;
+          for (int q = 0; q < QT; ++q) {
+#pragma unroll
+            for (int of = 4; of < 32; of <<= 1) {
+              bm0[q] = fmaxf(bm0[q], __shfl_xor_sync(0xffffffffu, bm0[q], of));
+              bm1[q] = fmaxf(bm1[q], __shfl_xor_sync(0xffffffffu, bm1[q], of));
+            }
+            const float n0 = fmaxf(m0[q], fmaxf(bm0[q], NEG_BIG)), n1 = fmaxf(m1[q], fmaxf(bm1[q], NEG_BIG));
+            const float al0 = fast_exp2((m0[q] - n0) * sc), al1 = fast_exp2((m1[q] - n1) * sc);
+            m0[q] = n0; m1[q] = n1;
+            mneg0[q] = -n0 * sc; mneg1[q] = -n1 * sc;
+            thr0[q] = n0 + tau_raw; thr1[q] = n1 + tau_raw;
+            l0[q] *= al0; l1[q] *= al1;
+#pragma unroll
+            for (int j = 0; j < Gm::KS; ++j) {
+              o[q][j][0] *= al0; o[q][j][1] *= al1; o[q][j][2] *= al0; o[q][j][3] *= al1;
+            }
           }
         }
 #pragma unroll
-        for (int bi = 0; bi < UB; ++bi) {
-          const float p00 = fast_exp2(fmaf(x[bi][0], sc, mneg0)), p01 = fast_exp2(fmaf(x[bi][1], sc, mneg1)),
-                      p10 = fast_exp2(fmaf(x[bi][2], sc, mneg0)), p11 = fast_exp2(fmaf(x[bi][3], sc, mneg1));
-          l0 += p00 + p10;
-          l1 += p01 + p11;
-          // transpose the two 8x8 (token, row) tiles
-          pb[bi][0] = movmatrix_trans(pack_f16x2(p00, p01));
-          pb[bi][1] = movmatrix_trans(pack_f16x2(p10, p11));
-        }
+        for (int q = 0; q < QT; ++q)
+#pragma unroll
+          for (int bi = 0; bi < UB; ++bi) {
+            const float p00 = fast_exp2(fmaf(x[q][bi][0], sc, mneg0[q])), p01 = fast_exp2(fmaf(x[q][bi][1], sc, mneg1[q])),
+                        p10 = fast_exp2(fmaf(x[q][bi][2], sc, mneg0[q])), p11 = fast_exp2(fmaf(x[q][bi][3], sc, mneg1[q]));
+            l0[q] += p00 + p10;
+            l1[q] += p01 + p11;
+            // transpose the two 8x8 (token, row) tiles
+            pb[q][bi][0] = movmatrix_trans(pack_f16x2(p00, p01));
+            pb[q][bi][1] = movmatrix_trans(pack_f16x2(p10, p11));
+          }
       };
 
       // ---------------- O^T += V^T P^T : rows = channels of block g (+8), columns = query rows
-      auto v_phase = [&](const uint32_t st, const uint32_t (&pb)[UB][2]) {
+      auto v_phase = [&](const uint32_t st, const uint32_t (&pb)[QT][UB][2]) {
         const uint32_t vd_ = st + voff_d, vs_ = st + voff_s;
 #pragma unroll
         for (int bi = 0; bi < UB; ++bi) {
@@ -706,9 +751,11 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
               e2m1x8_to_f16x2(ye, be);
               e2m1x8_to_f16x2(yo, bo);
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                mma_f16(o[8 * hf + 4 * wv + i], hmul2h(ae[i], sa), hmul2h(ao[i], sa), hmul2h(be[i], sb),
-                        hmul2h(bo[i], sb), pb[bi][0], pb[bi][1]);
+              for (int i = 0; i < 4; ++i) {
+                const uint32_t a0_ = hmul2h(ae[i], sa), a1_ = hmul2h(ao[i], sa), a2_ = hmul2h(be[i], sb), a3_ = hmul2h(bo[i], sb);
+#pragma unroll
+                for (int q = 0; q < QT; ++q) mma_f16(o[q][8 * hf + 4 * wv + i], a0_, a1_, a2_, a3_, pb[q][bi][0], pb[q][bi][1]);
+              }
             }
           }
         }
@@ -722,8 +769,8 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
         }
       } else if (wait_stage(bar, st)) {
         for (int blk = blk_first;;) {
-          float x[UB][4];
-          uint32_t pb[UB][2];
+          float x[QT][UB][4];
+          uint32_t pb[QT][UB][2];
           k_phase(st, x);
           softmax(st, blk, x, pb);
           v_phase(st, pb);
@@ -737,44 +784,48 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
 
     // ---------------- merge the TG warps' states of this piece and write it out
     {
-#pragma unroll
-      for (int of = 4; of < 32; of <<= 1) {
-        l0 += __shfl_xor_sync(0xffffffffu, l0, of);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, of);
-      }
       float sc = p.scale_log2 * __ldg(p.gk + h);
       sc = fmaxf(fabsf(sc), 1e-30f);
-      if (g == 0) {
-        mbuf[w * RPAD + 2 * c] = m0 * sc;          // log2 units from here on
-        mbuf[w * RPAD + 2 * c + 1] = m1 * sc;
-        lbuf[w * RPAD + 2 * c] = l0;
-        lbuf[w * RPAD + 2 * c + 1] = l1;
-      }
-      float* ob = obuf + (size_t)w * RPAD * Sm::OROW;
+      float* ob = obuf + (size_t)w * RP * Sm::OROW;
 #pragma unroll
-      for (int hf = 0; hf < Gm::NH; ++hf)
+      for (int q = 0; q < QT; ++q) {
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          const int ch = 16 * (g + 8 * hf) + 2 * jj;
-          const float* a = o[8 * hf + jj];
-          *reinterpret_cast<float2*>(ob + (2 * c) * Sm::OROW + ch) = make_float2(a[0], a[2]);
-          *reinterpret_cast<float2*>(ob + (2 * c + 1) * Sm::OROW + ch) = make_float2(a[1], a[3]);
+        for (int of = 4; of < 32; of <<= 1) {
+          l0[q] += __shfl_xor_sync(0xffffffffu, l0[q], of);
+          l1[q] += __shfl_xor_sync(0xffffffffu, l1[q], of);
         }
+        const int ra = 8 * q + 2 * c;              // this lane's rows of the tile: ra, ra + 1
+        if (g == 0) {
+          mbuf[w * RP + ra] = m0[q] * sc;          // log2 units from here on
+          mbuf[w * RP + ra + 1] = m1[q] * sc;
+          lbuf[w * RP + ra] = l0[q];
+          lbuf[w * RP + ra + 1] = l1[q];
+        }
+#pragma unroll
+        for (int hf = 0; hf < Gm::NH; ++hf)
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) {
+            const int ch = 16 * (g + 8 * hf) + 2 * jj;
+            const float* a = o[q][8 * hf + jj];
+            *reinterpret_cast<float2*>(ob + ra * Sm::OROW + ch) = make_float2(a[0], a[2]);
+            *reinterpret_cast<float2*>(ob + (ra + 1) * Sm::OROW + ch) = make_float2(a[1], a[3]);
+          }
+      }
       __syncthreads();
       const float gvh = __ldg(p.gv + h);
       const int slot_id = part * 2 + (piece_idx == 0 ? 0 : 1);
       // a thread stays on one query row (4 rows x 32 threads, or 8 x 16), so the warps' weights are worked out once
-      const int tpr = R <= RPAD / 2 ? NTHREADS / (RPAD / 2) : NTHREADS / RPAD;   // threads per row
+      const int tpr = R <= RP / 2 ? NTHREADS / (RP / 2) : NTHREADS / RP;   // threads per row
       const int row = tid / tpr;
       if (row < R) {
         float mx = -3.0e38f;
 #pragma unroll
-        for (int ww = 0; ww < TG; ++ww) mx = fmaxf(mx, mbuf[ww * RPAD + row]);
+        for (int ww = 0; ww < TG; ++ww) mx = fmaxf(mx, mbuf[ww * RP + row]);
         float den = 0.0f, wgt[TG];
 #pragma unroll
         for (int ww = 0; ww < TG; ++ww) {
-          wgt[ww] = fast_exp2(mbuf[ww * RPAD + row] - mx);
-          den += lbuf[ww * RPAD + row] * wgt[ww];
+          wgt[ww] = fast_exp2(mbuf[ww * RP + row] - mx);
+          den += lbuf[ww * RP + row] * wgt[ww];
         }
         const float inv = den > 0.0f ? gvh / den : 0.0f;
         const float* orow = obuf + (size_t)row * Sm::OROW;
@@ -784,14 +835,14 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
           const int t = (p.row0 + row) / G, gq = p.row0 + row - t * G;
           dst_o = p.out + ((long long)(q0 + t) * (KVH * G) + h * G + gq) * D;
         } else {
-          dst_p = opart_ws + ((size_t)slot_id * RPAD + row) * D;
-          if (tid == row * tpr) lse_ws[slot_id * RPAD + row] = den > 0.0f ? log2f(den) + mx : -__int_as_float(0x7f800000);
+          dst_p = opart_ws + ((size_t)slot_id * RP + row) * D;
+          if (tid == row * tpr) lse_ws[slot_id * RP + row] = den > 0.0f ? log2f(den) + mx : -__int_as_float(0x7f800000);
         }
         for (int ch = (tid - row * tpr) * 2; ch < D; ch += 2 * tpr) {
           float n0 = 0.0f, n1 = 0.0f;
 #pragma unroll
           for (int ww = 0; ww < TG; ++ww) {
-            const float2 v = *reinterpret_cast<const float2*>(orow + (size_t)ww * RPAD * Sm::OROW + ch);
+            const float2 v = *reinterpret_cast<const float2*>(orow + (size_t)ww * RP * Sm::OROW + ch);
             n0 += v.x * wgt[ww];
             n1 += v.y * wgt[ww];
           }
@@ -830,8 +881,10 @@ __global__ void __launch_bounds__(NTHREADS, Geo<D, LAYOUT>::MINB) decode_kernel(
       const long long seq_u0 = sq.seq0 + PC;
       const int first = (int)(seq_u0 / per), last = (int)((seq_u0 + sq.U - 1) / per);
       const int first_slot = (long long)first * per >= sq.seq0 ? 0 : 1;
-      merge_split<D, RPAD, NTHREADS>(lse_ws, opart_ws, first, last, first_slot, sq.R, p.row0, p.G,
-                     p.out + ((long long)sq.q0 * (KVH * p.G) + sq.h * p.G) * D, (long long)KVH * p.G * D, p.v_scale);
+      for (int rb = 0; rb < sq.R; rb += RPAD)
+        merge_split<D, RP, NTHREADS, RPAD>(lse_ws, opart_ws, first, last, first_slot, sq.R, p.row0, p.G,
+                                          p.out + ((long long)sq.q0 * (KVH * p.G) + sq.h * p.G) * D,
+                                          (long long)KVH * p.G * D, p.v_scale, rb);
     }
   }
 
@@ -851,18 +904,19 @@ int record_cuda(cudaError_t e);
 struct DeviceInfo {
   int sms = 0;
   int ctas_per_sm[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};    // [D == 256][LAYOUT]
+  int ctas_two_tiles = 0;                            // decode_kernel<128, 0, 2>: sixteen query rows per pass
   std::atomic<bool> ready{false};                    // set (release) after the fields above, under g_setup_mutex
 };
 static DeviceInfo g_dev[64];
 static std::mutex g_setup_mutex;                     // serialises the once-per-device set-up of concurrent host threads
 static std::atomic<int> g_early_metadata{0};
 
-template <int D, int LAYOUT>
+template <int D, int LAYOUT, int QT = 1>
 static cudaError_t setup_variant(int& ctas) {
-  auto k = decode_kernel<D, LAYOUT>;
-  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D, LAYOUT>::TOTAL);
+  auto k = decode_kernel<D, LAYOUT, QT>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<D, LAYOUT, QT>::TOTAL);
   if (e != cudaSuccess) return e;
-  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, k, NTHREADS, Smem<D, LAYOUT>::TOTAL);
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, k, NTHREADS, Smem<D, LAYOUT, QT>::TOTAL);
 }
 
 static int device_info(DeviceInfo** out) {
@@ -883,6 +937,7 @@ static int device_info(DeviceInfo** out) {
       if ((e = setup_variant<256, 2>(di.ctas_per_sm[1][2])) != cudaSuccess) return record_cuda(e);
       if ((e = setup_variant<128, 3>(di.ctas_per_sm[0][3])) != cudaSuccess) return record_cuda(e);
       if ((e = setup_variant<256, 3>(di.ctas_per_sm[1][3])) != cudaSuccess) return record_cuda(e);
+      if ((e = setup_variant<128, 0, 2>(di.ctas_two_tiles)) != cudaSuccess) return record_cuda(e);
       di.ready.store(true, std::memory_order_release);
     }
   }
@@ -904,7 +959,10 @@ extern "C" size_t hkv_decode_workspace_bytes(int B, int KVH, int G, int D, int q
   if (B < 1 || B > kMaxBatch || KVH < 1 || G < 1 || qlmax < 1 || G * qlmax > kMaxRows || (D != 128 && D != 256)) return 0;
   DeviceInfo* di;
   if (device_info(&di) != HKV_OK) return 0;
-  return WorkspaceLayout(max_parts(*di, D), RPAD, D).total;
+  size_t need = WorkspaceLayout(max_parts(*di, D), RPAD, D).total;
+  if (D == 128 && G * qlmax > RPAD)                 // head-major pages may take the two-tile kernel (16 rows per pass)
+    need = std::max(need, WorkspaceLayout(std::min(kMaxParts, di->sms * std::max(1, di->ctas_two_tiles)), 2 * RPAD, D).total);
+  return need;
 }
 
 static int decode_impl(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
@@ -962,13 +1020,16 @@ static int decode_impl(const void* q, const void* kd, const void* ksf, const voi
   DeviceInfo* di;
   int rc = device_info(&di);
   if (rc != HKV_OK) return rc;
-  const int cps = di->ctas_per_sm[D == 256][layout];
+  // head_dim 128, head-major slot pages, more than 8 query rows per kv head: the two-tile kernel serves 16 rows per pass
+  const bool two = D == 128 && layout == 0 && G * qlmax > RPAD && di->ctas_two_tiles > 0;
+  const int rows_per_pass = two ? 2 * RPAD : RPAD;
+  const int cps = two ? di->ctas_two_tiles : di->ctas_per_sm[D == 256][layout];
   if (cps < 1) return HKV_ERR_UNSUPPORTED;
   (void)max_parts;
   long long n_parts = std::min<long long>((long long)di->sms * cps, kMaxParts);
   if (splits > 0) n_parts = std::min<long long>(n_parts, (long long)B * KVH * splits);
   if (n_parts < 1) n_parts = 1;
-  if (workspace_bytes < WorkspaceLayout((int)n_parts, RPAD, D).total) return HKV_ERR_WORKSPACE;
+  if (workspace_bytes < WorkspaceLayout((int)n_parts, rows_per_pass, D).total) return HKV_ERR_WORKSPACE;
   DecodeParams p;
   p.q = (const __nv_bfloat16*)q;
   p.kd = (const uint8_t*)kd; p.ksf = (const uint8_t*)ksf; p.vd = (const uint8_t*)vd; p.vsf = (const uint8_t*)vsf;
@@ -988,17 +1049,18 @@ static int decode_impl(const void* q, const void* kd, const void* ksf, const voi
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned grid = (unsigned)n_parts;
   void (*k)(const DecodeParams) =
+      two ? decode_kernel<128, 0, 2> :
       D == 128 ? (layout == 0 ? decode_kernel<128, 0> : layout == 1 ? decode_kernel<128, 1> : decode_kernel<128, 3>)
                : (layout == 0 ? decode_kernel<256, 0> : layout == 1 ? decode_kernel<256, 1>
                   : layout == 2 ? decode_kernel<256, 2> : decode_kernel<256, 3>);
-  const size_t smem_bytes = D == 128 ? (size_t)Smem<128, 0>::TOTAL
+  const size_t smem_bytes = two ? (size_t)Smem<128, 0, 2>::TOTAL : D == 128 ? (size_t)Smem<128, 0>::TOTAL
                                      : layout == 2 ? (size_t)Smem<256, 2>::TOTAL : (size_t)Smem<256, 0>::TOTAL;
   static_assert(Smem<128, 0>::TOTAL == Smem<128, 1>::TOTAL && Smem<256, 0>::TOTAL == Smem<256, 1>::TOTAL &&
                 Smem<128, 0>::TOTAL == Smem<128, 3>::TOTAL && Smem<256, 0>::TOTAL == Smem<256, 3>::TOTAL,
                 "layouts share a size");
-  // More than RPAD query rows per kv head (large groups, several draft tokens) are served RPAD rows at a time: every
+  // More query rows per kv head than a pass serves (large groups, several draft tokens) take several passes: every
   // pass is one launch over the cache (split sequences are merged inside it).
-  for (int row0 = 0; row0 < G * qlmax; row0 += RPAD) {
+  for (int row0 = 0; row0 < G * qlmax; row0 += rows_per_pass) {
     p.row0 = row0;
     rc = record_cuda(launch_pdl(k, dim3(grid), dim3(NTHREADS), smem_bytes, st, p));
     if (rc != HKV_OK) return rc;

@@ -7,7 +7,7 @@ module is what the ncu summaries of the other kernels and variants are captured 
     python -m horizon_kernels_b200.microbench dequant [--tokens 262144] [--kvh 8] [--d 128] [--iters 10] [--f16]
     python -m horizon_kernels_b200.microbench pipes
     python -m horizon_kernels_b200.microbench decode  [--batch 192] [--kvh 2] [--g 8] [--d 256] [--min-len 128]
-                                                      [--max-len 32768] [--iters 10] [--had] [--k8] [--nhd]
+                                                      [--max-len 32768] [--iters 10] [--had] [--k8] [--nhd] [--ql 1]
 """
 import argparse
 import json
@@ -121,18 +121,20 @@ def decode(a):
         v = torch.randn(n, KVH, D, generator=g, device="cuda")
         sl = (pg[:, None] * PS + torch.arange(PS, device="cuda")[None, :]).reshape(-1)
         K.write(k.to(torch.bfloat16), v.to(torch.bfloat16), flat, st, PS, sl, gk, gv, False, signs=signs, k8=a.k8)
-    q = torch.randn(B, KVH * G, D, generator=g, device="cuda").to(torch.bfloat16)
+    ql = a.ql                                      # query tokens per request (1 + draft tokens), causal among themselves
+    q = torch.randn(B * ql, KVH * G, D, generator=g, device="cuda").to(torch.bfloat16)
     sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
-    qsl = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+    qsl = torch.arange(B + 1, dtype=torch.int32, device="cuda") * ql
     out = torch.empty_like(q)
-    ws = K.alloc_workspace(B, KVH, G, D, 1, "cuda")
-    ms = _time(lambda: K.decode_ragged(q, flat, st, PS, bt, sl, qsl, D ** -0.5, 1.0, gk, gv, 1, out, ws, signs=signs,
+    ws = K.alloc_workspace(B, KVH, G, D, ql, "cuda")
+    ms = _time(lambda: K.decode_ragged(q, flat, st, PS, bt, sl, qsl, D ** -0.5, 1.0, gk, gv, ql, out, ws, signs=signs,
                                        k8=a.k8), a.iters)
     if K.workspace_status(ws) != 0 or not bool(torch.isfinite(out.float()).all()):
         raise RuntimeError("decode reported a wait that ran out, or a non-finite output")
     byts = sum(lens) * KVH * _token_bytes(D, a.k8)
     print(json.dumps({"kernel": "decode", "batch": B, "kv_heads": KVH, "group": G, "head_dim": D,
-                      "rotated": a.had, "k8": a.k8, "positions_outermost_pages": a.nhd, "cached_tokens": sum(lens), "cache_mb": byts / 1e6,
+                      "rotated": a.had, "k8": a.k8, "positions_outermost_pages": a.nhd, "query_tokens": ql,
+                      "query_rows_per_kv_head": G * ql, "cached_tokens": sum(lens), "cache_mb": byts / 1e6,
                       "us": ms * 1e3, "algorithmic_gbs": byts / ms / 1e6}))
 
 
@@ -169,6 +171,7 @@ def main():
     ap.add_argument("--max-len", type=int, default=32768)
     ap.add_argument("--had", action="store_true", help="rotated keys (sign flips + Hadamard transform)")
     ap.add_argument("--k8", action="store_true", help="the FP8-key slot (head_dim 256)")
+    ap.add_argument("--ql", type=int, default=1, help="decode: query tokens per request (group x ql rows per kv head)")
     ap.add_argument("--nhd", action="store_true", help="decode: pages with positions outermost (row-copy path)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--f16", action="store_true")

@@ -84,8 +84,9 @@ size_t hkv_decode_workspace_bytes(int B, int KVH, int G, int D, int qlmax);
  *   block_tables : int32 (B, MP); seq_lens int32 (B); query_start_loc int32 (B + 1)
  *   requests with 0 or more than qlmax query tokens are skipped and their output rows left untouched
  *   out          : bf16 (>= n_tokens, KVH*G, D) contiguous
- * A pass over the cache serves 8 query rows per kv head. G * qlmax <= 8 is one launch. Up to 64 rows are accepted:
- * the call then makes ceil(G * qlmax / 8) launches.
+ * A pass over the cache serves 8 query rows per kv head, or 16 at head_dim 128 over head-major slot pages (the reference
+ * serves up to 32 rows in one launch, backend.py:237). G * qlmax within one pass is one launch. Up to 64 rows are
+ * accepted: the call then makes ceil(G * qlmax / rows per pass) launches.
  */
 int hkv_decode(const void* q, const void* kd, const void* ksf, const void* vd, const void* vsf,
                const int64_t strides[6], int PS, const int32_t* block_tables, int MP, const int32_t* seq_lens,

@@ -181,7 +181,7 @@ def test_long_context_split_and_combine():
     print("64k errors", mx, mn, rl)
 
 
-@pytest.mark.parametrize("D,KVH,G", [(128, 2, 4), (256, 1, 8)])
+@pytest.mark.parametrize("D,KVH,G", [(128, 2, 4), (256, 1, 8), (128, 2, 8)])
 def test_every_sequence_split_over_three_or_more_partitions(D, KVH, G):
     """few long sequences on a grid that fills the GPU: every sequence is cut into many pieces (hundreds of partitions
     over 2 to 4 sequences), each merged inside the decode launch by whichever CTA finishes its last piece. The result
@@ -189,9 +189,11 @@ def test_every_sequence_split_over_three_or_more_partitions(D, KVH, G):
     launch, and a cap on the partitions (`splits` 1 / 2 / 64, i.e. 1, 2 and up to 64 pieces per sequence) stays within
     the tolerance."""
     lens = [9000, 12345]
-    c = build_decode_case(2210 + D, lens, KVH, G, D, 16, ql_list=[1, 2] if G * 2 <= 8 else None)
+    one_pass = 16 if D == 128 else 8                  # query rows per kv head a single pass serves
+    two = G * 2 <= one_pass                            # (group 8 x 2 tokens at head_dim 128: the sixteen-row kernel)
+    c = build_decode_case(2210 + D + G, lens, KVH, G, D, 16, ql_list=[1, 2] if two else None)
     ref = oracle_decode(c, v_scale=0.5)
-    qlmax = 2 if G * 2 <= 8 else 1
+    qlmax = 2 if two else 1
     out, ws = gpu_decode(c, v_scale=0.5, qlmax=qlmax)
     assert K.workspace_status(ws) == 0
     assert_close(out, ref)
