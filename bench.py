@@ -53,8 +53,8 @@ REPEATS = 11                      # replays behind every median of the kernel-on
 # DRAM bytes (read + written) per algorithmic byte of one decode launch, from the ncu captures summarised under
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over sum(L) * KVH * D * 1.125); c4's capture is one rank's
 # share of the batch at 8 GPUs (same length law), and traffic grows in proportion to the cached tokens
-TRAFFIC_RATIO = {"c1": (330.123 + 4.825) / 328.42, "c2": (1209.754 + 4.464) / 1207.960,
-                 "c4": (564.456 + 6.078) / 560.241}
+TRAFFIC_RATIO = {"c1": (296.768 + 5.083) / 297.3, "c2": (1210.028 + 3.940) / 1207.960,
+                 "c4": (565.765 + 5.784) / 560.241}
 
 
 def draw_lens(cfg, seed):
