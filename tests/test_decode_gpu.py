@@ -352,3 +352,28 @@ def test_minimal_workspace_of_a_capped_split_count():
     torch.cuda.synchronize()
     assert (buf[need:] == 0xA5).all()
     assert_close(out, oracle_decode(c))
+
+
+@pytest.mark.parametrize("D", [128, 256])
+def test_pieces_in_which_some_rows_see_no_key(D):
+    """one long sequence on a grid that gives (nearly) every unit its own partition, eight query tokens on one head: the
+    last unit holds three tokens, which only the last three query tokens may see, so for the other rows that piece is
+    empty (log-sum-exp -inf, its partial must be ignored by the merge); plus a request whose context is shorter than its
+    query tokens, whose first rows see nothing at all and must come out as zeros"""
+    UT = 32 if D == 128 else 16
+    sms = K.num_sms()
+    n_units = sms * (3 if D == 128 else 2) - (12 if D == 128 else 24) - 2      # about one unit per partition
+    lens = [UT * n_units + 3, 5]
+    c = build_decode_case(2700 + D, lens, 1, 1, D, 16, ql_list=[8, 8])
+    ref = oracle_decode(c)
+    out, ws = gpu_decode(c, qlmax=8)
+    assert K.workspace_status(ws) == 0
+    got = out.float().cpu().numpy()
+    q1 = int(c["qsl"][1])
+    # request 1: context 5, 8 query tokens: token t sees 5 - 8 + t + 1 keys, none for t < 3
+    assert (got[q1:q1 + 3] == 0).all()
+    ref2 = ref.copy()
+    ref2[q1:q1 + 3] = 0.0                                        # (the oracle leaves rows without keys as NaN or zero)
+    assert_close(out, np.nan_to_num(ref2, nan=0.0))
+    o2, _ = gpu_decode(c, ws=ws, qlmax=8)
+    assert torch.equal(out, o2)
