@@ -1,6 +1,6 @@
 // Paged split-K flash-decoding over the NVFP4 KV cache, and the log-sum-exp combine (sm_100a).
 //
-// Work decomposition ("balanced split-K"): the unit of work is UT consecutive tokens (32 at head_dim 128, 16 at 256)
+// Work decomposition ("balanced split-K"): the unit of work is UT consecutive tokens (32; 16 for the K8V4 slot)
 // of one (request, kv head) sequence. All units of a batch, ordered (request, kv head, position), form one stream that
 // is cut into equal partitions, one per CTA of a grid that fills the GPU exactly once. A CTA therefore streams the same
 // number of cache bytes as every other CTA whatever the mix of context lengths. Inside a partition, a run of units of
@@ -54,9 +54,9 @@ constexpr int RPAD = 8;          // query rows per (request, kv head) of one pas
 template <int D, int LAYOUT>
 struct Geo {
   static constexpr int SD = D / 2, SS = D / 16, SLOT = SD + SS;
-  static constexpr int UB = D == 128 ? 2 : 1;          // 16-token blocks per unit
+  static constexpr int UB = (D == 128 || LAYOUT != 2) ? 2 : 1;   // 16-token blocks per unit (1 for the K8V4 slot)
   static constexpr int UT = 16 * UB, LOG_UT = UB == 2 ? 5 : 4;
-  static constexpr int NS = D == 128 ? 3 : LAYOUT == 2 ? 3 : 4;   // stages per warp
+  static constexpr int NS = D == 128 ? 3 : LAYOUT == 2 ? 3 : 2;   // stages per warp
   static constexpr int MINB = D == 128 ? 3 : 2;        // CTAs per SM the register budget is sized for
   static constexpr bool K8 = LAYOUT == 2;
   static constexpr int SLOT8 = D + SD + SS;            // K8V4 slot: 400 bytes at head_dim 256
@@ -73,11 +73,11 @@ struct Geo {
   // What a sequence costs a partition beyond its units (locating it, loading its queries, the end-of-piece merge and
   // the output), in units: measured 3 to 4 microseconds per piece. The stream that is cut into equal partitions counts
   // every sequence as PIECE_COST + its units, so partitions that hold many short sequences get fewer units.
-  static constexpr int PIECE_COST = D == 128 ? 12 : 24;
+  static constexpr int PIECE_COST = UB == 2 ? 12 : 24;
   static constexpr int KS = D / 16;                    // k-steps of K Q^T == mma tiles of V^T P^T (per 16 tokens)
   static constexpr int NBL = D / 64;                   // 16-channel blocks of one key row held by one lane
   static constexpr int NH = D / 128;                   // 16-channel blocks of one value row held by one lane
-  static constexpr int NCH = UB == 1 ? 2 : 1;          // independent accumulators per score tile
+  static constexpr int NCH = D == 256 ? 2 : 1;          // independent accumulators per score tile
   // token (row of a 16-token block) handled by row i of the 16-row score tile. With 72-byte rows (head_dim 128, slot
   // layout) bits 1 and 3 of i are swapped: then the key loads of a half warp (rows i = 4k .. 4k+3, 16 bytes apart
   // inside a row) and its value loads (rows i = j, j+2, j+4, j+6, 32 contiguous bytes of each) both touch every

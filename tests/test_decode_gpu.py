@@ -360,9 +360,9 @@ def test_pieces_in_which_some_rows_see_no_key(D):
     last unit holds three tokens, which only the last three query tokens may see, so for the other rows that piece is
     empty (log-sum-exp -inf, its partial must be ignored by the merge); plus a request whose context is shorter than its
     query tokens, whose first rows see nothing at all and must come out as zeros"""
-    UT = 32 if D == 128 else 16
+    UT = 32                                              # tokens of a unit of the stream
     sms = K.num_sms()
-    n_units = sms * (3 if D == 128 else 2) - (12 if D == 128 else 24) - 2      # about one unit per partition
+    n_units = sms * (3 if D == 128 else 2) - 12 - 2      # about one unit per partition (a sequence weighs its units + 12)
     lens = [UT * n_units + 3, 5]
     c = build_decode_case(2700 + D, lens, 1, 1, D, 16, ql_list=[8, 8])
     ref = oracle_decode(c)
