@@ -293,7 +293,18 @@ def time_decode_kernel(w, launches, local, seconds=0.35):
             dgraph.replay()
         torch.cuda.synchronize()
     return {"back_to_back_ms": stats(b2b), "isolated_ms": stats(iso), "launches_per_replay": launches,
-            "clocks": sampler.summary()}
+            "clocks": sampler.summary(), "b2b_samples": b2b, "iso_samples": iso, "clock_samples": list(sampler.samples)}
+
+
+def merge_timings(a, b):
+    """two legs of time_decode_kernel (before and after the timed steps) as one record: under the power cap the SM clock
+    wanders by 10 to 15 % over seconds, so the kernel is sampled on both sides of the region it is compared with"""
+    b2b, iso, clk = a["b2b_samples"] + b["b2b_samples"], a["iso_samples"] + b["iso_samples"], sorted(
+        a["clock_samples"] + b["clock_samples"])
+    return {"back_to_back_ms": stats(b2b), "isolated_ms": stats(iso), "launches_per_replay": a["launches_per_replay"],
+            "clocks": {"sm_mhz": clk[len(clk) // 2] if clk else None, "sm_max_mhz": a["clocks"]["sm_max_mhz"],
+                       "reasons": sorted(set(a["clocks"]["reasons"]) | set(b["clocks"]["reasons"])), "samples": len(clk)},
+            "b2b_samples": b2b, "iso_samples": iso, "clock_samples": clk}
 
 
 def roofline_record(w, t, peak, peak_src):
@@ -306,6 +317,7 @@ def roofline_record(w, t, peak, peak_src):
             "workload": w.name, "algorithmic_bytes_per_launch": alg, "kernel_ms": ms,
             "kernel_ms_min": t["back_to_back_ms"]["min"], "kernel_ms_max": t["back_to_back_ms"]["max"],
             "repeats": t["back_to_back_ms"]["n"], "launches_per_replay": t["launches_per_replay"],
+            "kernel_ms_samples": [round(x, 5) for x in t["b2b_samples"]],
             "frac_of_nominal_8tbs": achieved / 8000.0,
             "isolated_kernel_ms": iso, "isolated_kernel_ms_min": t["isolated_ms"]["min"],
             "isolated_kernel_ms_max": t["isolated_ms"]["max"], "frac_isolated": alg / (iso * 1e-3) / 1e9 / peak,
@@ -547,12 +559,12 @@ def main():
         while time.perf_counter() < t_end:
             graphs[i % NBT].replay()
             i += 1
-        # ---- the decode kernel alone (roofline), before the timed steps: the clocks still sink slowly under sustained
-        # load, so whatever is timed later runs a little slower; this order keeps "kernel <= step" what it physically is
+        # ---- the decode kernel alone (roofline): one leg before the timed steps and one after them (merged below)
         kt = time_decode_kernel(w, min(args.steps, 20), local, seconds=0.2)
         for i in range(args.warmup):
             graphs[i % NBT].replay()
         barrier()
+        n_clk0 = len(sampler.samples)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(units) + 1)]
         ev[0].record()
         for j, (g, _) in enumerate(units):
@@ -561,6 +573,8 @@ def main():
         barrier()
         ms_total = ev[0].elapsed_time(ev[-1])
         unit_ms = [ev[j].elapsed_time(ev[j + 1]) / n for j, (_, n) in enumerate(units)]
+        clk_steps = sorted(sampler.samples[n_clk0:])                 # SM clock samples of the timed steps alone
+        kt = merge_timings(kt, time_decode_kernel(w, min(args.steps, 20), local, seconds=0.1))
 
         # ---- end to end: host inputs -> one pinned H2D copy -> write + decode (graph) -> D2H of the output.
         # The step's inputs (query, new K/V rows, slot ids, context lengths, query offsets, block tables) sit back to
@@ -721,10 +735,12 @@ def main():
                               if NBT > 1 else "one batch whose cache reads per GPU exceed the L2 several times"),
                        "timing": ("CUDA graphs of the plugin calls (5 steps per batch chained in one graph, like the layers "
                                   "of a model), CUDA events around the K steps, max over ranks; roofline: decode launches "
-                                  f"back to back in one graph, CUDA events around a replay, median of {REPEATS} replays"),
+                                  f"back to back in one graph, CUDA events around a replay, median of 2 x {REPEATS} replays, half of them "
+                                  "before and half after the timed steps"),
                        "clocks": "NVML sampled every 20 ms while the same step loops before, during and after the timed steps"},
             "tokens_per_s_per_gpu": value / world,
-            "step_samples": {"ms_per_step": stats(unit_ms), "unit": "replay units of the timed region on rank 0"},
+            "step_samples": {"ms_per_step": stats(unit_ms), "unit": "replay units of the timed region on rank 0",
+                             "sm_mhz": clk_steps[len(clk_steps) // 2] if clk_steps else None},
             "roofline": roof, **extra,
             "step_hbm_gbs": alg / (ms_step * 1e-3) / 1e9,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
