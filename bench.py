@@ -554,6 +554,11 @@ def main():
         # the GPU is kept under the same load before and after the timed steps so that the 20 ms clock samples see it,
         # and long enough before them for the clocks to settle where the power cap leaves them (they sink for a second
         # or two after a cold start: timed too early, the steps would look faster than the kernel timed after them)
+        # Ranks reach this point seconds apart (rank 0 timed configurations 1 and 2, the communicator comes up inside
+        # the first collective): the barrier HERE absorbs that wait, so that every rank enters the load below at the
+        # same moment and the barrier in front of the timed steps waits for milliseconds of skew, not for an idle gap
+        # after which the clocks would boost for the few milliseconds the steps take.
+        barrier()
         t_end = time.perf_counter() + 2.0
         i = 0
         while time.perf_counter() < t_end:

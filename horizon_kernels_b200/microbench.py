@@ -139,24 +139,26 @@ def decode(a):
 
 
 def pipes(a):
-    """cycles per warp instruction and SM sub-partition for the instruction kinds of the decode kernel
+    """cycles per warp instruction and SM sub-partition for the instruction kinds of the decode and write kernels
     (hkv_probe_issue_rates in include/hkv.h), at 1, 3 and 4 warps per sub-partition"""
     import ctypes as C
     from . import _lib
     names = ["cvt.rn.f16x2.e2m1x2", "mul.f16x2", "fma.f32", "lop3", "4 cvt + 4 mul.f16x2", "4 cvt + 4 mul + 1 add",
-             "4 cvt + 4 mul + 1 add + mma.m16n8k16"]
-    per_rep = [8, 8, 8, 8, 8, 9, 10]
-    nbytes = 7 * 256 * 8 + 256 * 1024 * 4
+             "4 cvt + 4 mul + 1 add + mma.m16n8k16", "mul.f32", "mul.f32x2", "cvt.rn.satfinite.e2m1x2.f32",
+             "cvt.f32.f16", "prmt"]
+    per_rep = [8, 8, 8, 8, 8, 9, 10, 8, 8, 8, 8, 8]
+    M = len(names)
+    nbytes = M * 256 * 8 + 256 * 1024 * 4
     buf = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     for wps in (1, 3, 4):
         _lib.check(_lib.load().hkv_probe_issue_rates(C.c_void_p(buf.data_ptr()), nbytes, wps,
                                                      C.c_void_p(torch.cuda.current_stream().cuda_stream)), "hkv_probe_issue_rates")
         torch.cuda.synchronize()
-        cyc = buf[:7 * 256 * 8].view(torch.int64).view(7, 256)[:, :sms].double().mean(dim=1).cpu().tolist()
+        cyc = buf[:M * 256 * 8].view(torch.int64).view(M, 256)[:, :sms].double().mean(dim=1).cpu().tolist()
         print(json.dumps({"kernel": "pipes", "warps_per_subpartition": wps, "cycles_per_warp_instruction": {
             n: round(c / (2048 * k * wps), 3) for n, c, k in zip(names, cyc, per_rep)},
-            "cycles_per_repetition": {n: round(c / (2048 * wps), 2) for n, c in zip(names[4:], cyc[4:])}}))
+            "cycles_per_repetition": {n: round(c / (2048 * wps), 2) for n, c in zip(names[4:7], cyc[4:7])}}))
 
 
 def main():

@@ -238,16 +238,17 @@ int hkv_selftest_codec(void* out, size_t out_bytes, void* stream);
 
 /*
  * Issue-rate probe, no counterpart in the reference: times, with the SM clock counter, unrolled sequences of the
- * instruction kinds the decode kernel is made of, `warps_per_subpartition` (1..8) warps per SM sub-partition, one block
- * per SM. Results in `scratch` (device memory, 8-byte aligned, HKV_PROBE_SCRATCH_BYTES): int64 cycles[7][256], entry
+ * instruction kinds the decode and write kernels are made of, `warps_per_subpartition` (1..8) warps per SM sub-partition, one block
+ * per SM. Results in `scratch` (device memory, 8-byte aligned, HKV_PROBE_SCRATCH_BYTES): int64 cycles[12][256], entry
  * [mode][sm] = cycles that SM's block took for 2048 repetitions per warp of
  *   mode 0: 8 cvt.rn.f16x2.e2m1x2   1: 8 mul.f16x2   2: 8 fma.f32   3: 8 lop3   4: 4 conversions + 4 multiplies
  *   mode 5: 4 conversions + 4 multiplies + 1 integer add (the decode kernel's dequantise group without its mma)
  *   mode 6: mode 5 + one mma.sync.m16n8k16 (10 instructions per repetition)
+ *   mode 7: 8 mul.f32   8: 8 mul.f32x2   9: 8 cvt.rn.satfinite.e2m1x2.f32   10: 8 cvt.f32.f16   11: 8 prmt
  * cycles / (2048 * instructions per repetition * warps_per_subpartition) = cycles per warp instruction and
  * sub-partition. `python -m horizon_kernels_b200.microbench pipes` prints them. Asynchronous on the stream.
  */
-#define HKV_PROBE_SCRATCH_BYTES (7 * 256 * 8 + 256 * 1024 * 4)
+#define HKV_PROBE_SCRATCH_BYTES (12 * 256 * 8 + 256 * 1024 * 4)
 int hkv_probe_issue_rates(void* scratch, size_t scratch_bytes, int warps_per_subpartition, void* stream);
 
 /*

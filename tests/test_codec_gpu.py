@@ -70,15 +70,17 @@ def test_issue_rate_probe_runs_and_orders_the_pipes():
     """the probe behind the decode kernel's design notes: fp32 fma issues at full rate, the E2M1 conversion and the f16x2
     multiply at about half of it, and the dequantise group costs more with its warp-level mma than without"""
     L = _lib.load()
-    nbytes = 7 * 256 * 8 + 256 * 1024 * 4
+    M = 12
+    nbytes = M * 256 * 8 + 256 * 1024 * 4
     buf = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
     assert L.hkv_probe_issue_rates(C.c_void_p(buf.data_ptr()), nbytes, 4, None) == 0
     torch.cuda.synchronize()
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    cyc = buf[:7 * 256 * 8].view(torch.int64).view(7, 256)[:, :sms].double().mean(dim=1).cpu().numpy()
-    per = cyc / (2048 * np.array([8, 8, 8, 8, 8, 9, 10]) * 4)
+    cyc = buf[:M * 256 * 8].view(torch.int64).view(M, 256)[:, :sms].double().mean(dim=1).cpu().numpy()
+    per = cyc / (2048 * np.array([8, 8, 8, 8, 8, 9, 10, 8, 8, 8, 8, 8]) * 4)
     assert (per > 0.2).all() and (per < 20).all()
     assert per[2] < per[0] and per[2] < per[1]                 # fma.f32 is faster than the conversion and the f16x2 multiply
     assert cyc[6] > cyc[5]                                     # the mma adds issue time to the group
+    assert per[8] < 1.9 * per[7]                               # a packed mul.f32x2 costs less than two fp32 multiplies
     assert L.hkv_probe_issue_rates(C.c_void_p(buf.data_ptr()), nbytes, 9, None) == -6
     assert L.hkv_probe_issue_rates(C.c_void_p(buf.data_ptr()), 16, 4, None) == -5
