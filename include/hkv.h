@@ -229,11 +229,23 @@ int hkv_selftest_wait_timeout(void* workspace, int64_t cycles, void* stream);
  *               the hardware conversion the write kernel uses (cvt.rn.satfinite.e2m1x2.f32) than from the reference's
  *               threshold chain (kv_fp4_ref.py:122-130); must be 0
  *   uint64 [1]  the same count over the NaN patterns above +inf
+ *   uint64 [2]  how many (value, scale) pairs get a different quotient from the write kernel's three multiply-adds with
+ *               the scale's reciprocal than from an IEEE division (any bit where the quotient is >= 0.125, the E2M1
+ *               code everywhere); must be 0. Scales: every E4M3 code 1..126 times 64 global scales (few mantissa bits,
+ *               full mantissas, n / 2688, mantissas of all ones); values: the bf16 patterns of 17 binades around the
+ *               scale, hashed fp32 quotients in [0, 8), the seven rounding boundaries with their neighbours
+ *   uint64 [3]  the number of pairs compared (about 6 * 10^7)
+ *   uint64 [4]  how many blocks of 16 values get different codes, or a squared error that differs in any bit, from the
+ *               write kernel's packed fp32 pair arithmetic than from IEEE divisions, the threshold chain and the
+ *               reference's chain of single fp32 multiplies, subtractions and additions in index order
+ *               (kv_fp4_ref.py:148-156); must be 0
+ *   uint64 [5]  the number of blocks compared (about 2 * 10^6)
+ *   uint64 [6], [7]  zero
  *   uint16 [16 * 256]  f16 bits of cvt.rn.f16x2.e2m1x2(code) * cvt.rn.f16x2.e4m3x2(scale byte), index code * 256 + byte:
  *               the dequantised value the decode and dequantisation kernels form
  * A few milliseconds of GPU time; asynchronous on the stream like every other call.
  */
-#define HKV_SELFTEST_CODEC_BYTES (16 + 16 * 256 * 2)
+#define HKV_SELFTEST_CODEC_BYTES (64 + 16 * 256 * 2)
 int hkv_selftest_codec(void* out, size_t out_bytes, void* stream);
 
 /*

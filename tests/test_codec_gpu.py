@@ -4,7 +4,8 @@
 the formulas are machine instructions, so the check has to run where they execute.
 
   * write side: cvt.rn.satfinite.e2m1x2.f32 against the reference's threshold chain (kv_fp4_ref.py:122-130) for EVERY
-    non-negative fp32 bit pattern from 0 to +inf;
+    non-negative fp32 bit pattern from 0 to +inf; the quotient by three multiply-adds with the scale's reciprocal
+    against the IEEE division the reference performs, over 6 * 10^7 (value, scale) pairs;
   * read side: cvt.rn.f16x2.e2m1x2(code) * cvt.rn.f16x2.e4m3x2(scale byte) in f16 against e2m1_value * e4m3_value for
     all 16 codes x 256 scale bytes (the product is exact in f16); 0x7f / 0xff are NaN in E4M3 and stay NaN."""
 import ctypes as C
@@ -17,7 +18,7 @@ from horizon_kernels_b200 import _lib
 
 pytestmark = pytest.mark.gpu
 
-NBYTES = 16 + 16 * 256 * 2
+NBYTES = 64 + 16 * 256 * 2
 
 
 @pytest.fixture(scope="module")
@@ -28,7 +29,7 @@ def selftest():
     assert rc == 0
     torch.cuda.synchronize()
     host = buf.cpu().numpy()
-    return host[:16].view(np.uint64), host[16:].view(np.uint16).reshape(16, 256)
+    return host[:64].view(np.uint64), host[64:].view(np.uint16).reshape(16, 256)
 
 
 def test_hardware_e2m1_encode_equals_the_threshold_chain_for_every_non_negative_float(selftest):
@@ -36,6 +37,24 @@ def test_hardware_e2m1_encode_equals_the_threshold_chain_for_every_non_negative_
     assert int(counts[0]) == 0          # 0 .. +inf: 2^31 - 2^23 + 1 bit patterns, none differs
     # NaN inputs: the threshold chain saturates them to code 7 (every comparison is false) and so does the hardware
     assert int(counts[1]) == 0
+
+
+def test_quotient_by_multiply_adds_equals_the_division(selftest):
+    """the write kernel never divides a value by its scale: y0 = a * r, rem = fma(-s, y0, a), q = fma(rem, r, y0) with
+    r = RN(1 / s); the result must be the IEEE quotient the reference computes (kv_fp4_ref.py:159-186)"""
+    counts, _ = selftest
+    assert int(counts[3]) > 5 * 10 ** 7          # the pairs that were inside the fast path's range and compared
+    assert int(counts[2]) == 0
+
+
+def test_packed_pair_error_sum_equals_the_chain_of_single_operations(selftest):
+    """codes and squared error of a block from the packed fp32 pair instructions (mul.f32x2 / fma.f32x2) against the
+    reference's order of single IEEE operations (kv_fp4_ref.py:148-156): bit-equal, so the scale search picks the same
+    candidate even where two errors differ by one ulp (an assembler that contracts a packed multiply with the packed
+    subtraction after it rounds once instead of twice and fails this)"""
+    counts, _ = selftest
+    assert int(counts[5]) > 10 ** 6
+    assert int(counts[4]) == 0
 
 
 def test_dequantised_product_table_is_exact(selftest):
@@ -81,6 +100,6 @@ def test_issue_rate_probe_runs_and_orders_the_pipes():
     assert (per > 0.2).all() and (per < 20).all()
     assert per[2] < per[0] and per[2] < per[1]                 # fma.f32 is faster than the conversion and the f16x2 multiply
     assert cyc[6] > cyc[5]                                     # the mma adds issue time to the group
-    assert per[8] < 1.9 * per[7]                               # a packed mul.f32x2 costs less than two fp32 multiplies
+    assert 1.5 * per[7] < per[8] < 2.5 * per[7]                # a packed mul.f32x2 holds the pipe like two fp32 multiplies
     assert L.hkv_probe_issue_rates(C.c_void_p(buf.data_ptr()), nbytes, 9, None) == -6
     assert L.hkv_probe_issue_rates(C.c_void_p(buf.data_ptr()), 16, 4, None) == -5
