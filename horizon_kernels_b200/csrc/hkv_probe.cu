@@ -2,8 +2,9 @@
 // the instruction kinds the decode kernel is made of. The design notes of the decode kernel rest on these figures (on
 // B200 the E2M1 conversion, logic ops and f16x2 multiplies issue every second cycle, fp32 fma every cycle; conversions
 // and f16x2 multiplies sit on different pipes and overlap; a warp-level mma.m16n8k16 adds little more than a cycle to a
-// dequantise group) and so do those of the write kernel (a packed mul.f32x2 takes one issue slot and holds the fp32 pipe for two
-// cycles; f16 -> f32 conversions, prmt and logic ops take two cycles each), so the probe ships with the library and anyone can re-measure them:
+// dequantise group) and so do those of the write kernel (a packed mul.f32x2 takes one issue slot and holds the fp32
+// pipe for two cycles; f16 -> f32 conversions, prmt and logic ops take two cycles each), so the probe ships with the
+// library and anyone can re-measure them:
 //     python -m horizon_kernels_b200.microbench pipes
 #include "hkv_common.cuh"
 

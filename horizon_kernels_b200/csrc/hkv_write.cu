@@ -7,9 +7,11 @@
 // live in two registers (a nibble each), produced eight at a time by the hardware E2M1 conversion.
 //
 // Bit-exactness: the result must equal the reference's PyTorch quantiser (kv_fp4_ref.py:159-186 `quantize_rows`,
-// rules at kv_fp4_ref.py:15-25) byte for byte. Every arithmetic step is therefore a single IEEE fp32 operation issued
-// through an explicit intrinsic (__fdiv_rn, __fmul_rn, __fsub_rn, __fadd_rn): no contraction into FMA, no fast-math.
-// The squared error is summed sequentially over i = 0..15 and a later candidate wins only on a strict "<".
+// rules at kv_fp4_ref.py:15-25) byte for byte. Every arithmetic step therefore produces the result of a single IEEE
+// fp32 operation, issued through an explicit intrinsic or an explicit .rn instruction: no fast-math, and no
+// contraction where the reference rounds twice (the one place the assembler would contract is written so that it
+// cannot, see sub_from). The squared error is summed sequentially over i = 0..15 and a later candidate wins only on a
+// strict "<".
 #include <cuda_bf16.h>
 
 #include <algorithm>
@@ -125,8 +127,8 @@ __device__ __forceinline__ uint32_t e2m1_codes8(float y0, float y1, float y2, fl
   return w;
 }
 
-// the same, and the E2M1 values of the eight codes as four f16x2 (value 2j in the low half of v[j]): the conversion back
-// reads the code bytes where the conversion forth left them
+// the same, and the E2M1 values of the eight codes as four f16x2 (value 2j in the low half of v[j]): the conversion
+// back reads the code bytes where the conversion forth left them
 __device__ __forceinline__ uint32_t e2m1_codes8_values(float y0, float y1, float y2, float y3, float y4, float y5,
                                                        float y6, float y7, uint32_t (&v)[4]) {
   uint32_t w;
@@ -212,7 +214,8 @@ __device__ __forceinline__ float codes_sse(const f32x2 (&AX)[8], const BlockCode
 __device__ __forceinline__ void score(const f32x2 (&AX)[8], float amax, float sc, BlockCodes& c, float& err,
                                       bool want_err) {
   if (div_ok(sc, amax)) {
-    c = want_err ? block_codes_fast<true>(AX, sc, __frcp_rn(sc), err) : block_codes_fast<false>(AX, sc, __frcp_rn(sc), err);
+    const float r = __frcp_rn(sc);
+    c = want_err ? block_codes_fast<true>(AX, sc, r, err) : block_codes_fast<false>(AX, sc, r, err);
   } else {                                        // rare: a zero or extreme scale
     c = block_codes_exact(AX, sc);
     if (want_err) err = codes_sse(AX, c, sc);
@@ -298,7 +301,8 @@ __global__ void __launch_bounds__(256) write_kernel(const WriteParams p) {
       m[i] = __hlt2_mask(*reinterpret_cast<const __nv_bfloat162*>(&ws[i]), __floats2bfloat162_rn(0.0f, 0.0f));
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const uint32_t a = __byte_perm(m[4 * h], m[4 * h + 1], 0x6420), b = __byte_perm(m[4 * h + 2], m[4 * h + 3], 0x6420);
+      const uint32_t a = __byte_perm(m[4 * h], m[4 * h + 1], 0x6420);
+      const uint32_t b = __byte_perm(m[4 * h + 2], m[4 * h + 3], 0x6420);
       // a = masks of values 0, 1, 2, 3 of the word (one byte each), b = those of values 4 .. 7
       const uint32_t even = __byte_perm(a, b, 0x6420), odd = __byte_perm(a, b, 0x7531);
       sg[h] = ((even & 0x08080808u) | (odd & 0x80808080u));
@@ -469,8 +473,8 @@ __global__ void selftest_e2m1_encode_kernel(unsigned long long* counts) {
 // counts[2]: (value, scale) pairs inside div_ok's range whose quotient by three multiply-adds (div2) differs from the
 // division instruction's: in any bit where the quotient is at least 0.125, in the E2M1 code everywhere. counts[3]: the
 // pairs compared. Scales: RN(e4m3 value * g) for the codes 1..126 and 64 global scales g = blockIdx.y (few mantissa
-// bits, hashed full mantissas, n / 2688, mantissas of all ones). Values per scale (blockIdx.x * blockDim.x + threadIdx.x
-// = 0 .. 8191): the bf16 patterns of the 17 binades around the scale, RN(u * s) for hashed u in [0, 8), and the seven
+// bits, hashed full mantissas, n / 2688, mantissas of all ones). Values per scale (index blockIdx.x * blockDim.x +
+// threadIdx.x = 0 .. 8191): the bf16 patterns of the 17 binades around the scale, RN(u * s) for hashed u in [0, 8), and the seven
 // rounding boundaries times s with their neighbours.
 __global__ void selftest_quotient_kernel(unsigned long long* counts) {
   const unsigned gi = blockIdx.y, vi = blockIdx.x * blockDim.x + threadIdx.x;
@@ -516,7 +520,7 @@ __global__ void selftest_block_error_kernel(unsigned long long* counts) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const unsigned hsh = (id * 16u + i) * 2654435761u + 0x9e3779b9u;
-    ax[i] = __uint_as_float(((120u + (hsh >> 24) % 10u) << 23) | ((hsh >> 8) & 0x7f0000u));   // bf16 patterns in [2^-7, 8)
+    ax[i] = __uint_as_float(((120u + (hsh >> 24) % 10u) << 23) | ((hsh >> 8) & 0x7f0000u));   // bf16, [2^-7, 8)
     if ((hsh & 31u) == 0u) ax[i] = 0.0f;
     amax = fmaxf(amax, ax[i]);
   }
