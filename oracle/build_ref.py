@@ -4,7 +4,7 @@ code: only tests and bench.py's CPU arm load what this makes.
 The reference's format specification and oracle for the NVFP4 KV-cache path is one pure-torch module,
 nvidia-sm120/horizon_kvfp4/kernels/kv_fp4_ref.py (no TileLang, no vLLM imports: kv_fp4_ref.py:3-5). It is byte-compiled
 from where it lies in the reference tree (the tree's location is the `reference_path` entry of BASELINE.json at the
-repository root) into oracle/_ref/kv_fp4_ref.pyc. No source is copied. The compiled module travels to a machine that
+repository root) into oracle/_ref/kv_fp4_ref.bytecode. No source is copied. The compiled module travels to a machine that
 has no reference tree and lets `bench.py --impl reference` time the reference's own code there; `load()` returns None
 when it has not been built, and the callers then fall back to the C restatement (oracle/kvfp4_oracle.c)."""
 import importlib.machinery
@@ -16,7 +16,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
-PYC = os.path.join(OUT_DIR, "kv_fp4_ref.pyc")
+PYC = os.path.join(OUT_DIR, "kv_fp4_ref.bytecode")      # not "*.pyc": snapshot tools commonly skip that suffix
 REL = os.path.join("nvidia-sm120", "horizon_kvfp4", "kernels", "kv_fp4_ref.py")
 _mod = None
 
