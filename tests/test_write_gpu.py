@@ -79,6 +79,33 @@ def test_write_matches_oracle(D, KVH, PS, kind):
                 assert np.array_equal(cache.bytes(), got)
 
 
+@pytest.mark.parametrize("kind", ["edge", "outlier"])
+@pytest.mark.parametrize("D,KVH", [(128, 8), (256, 2)])
+def test_large_launch_one_lane_per_block_matches_oracle(D, KVH, kind):
+    """more than 4096 tokens: the launch gives every block to ONE lane, which scores the four scale candidates itself
+    (packed fp32 pairs, quotients by multiply-adds) and falls back to IEEE divisions for zero blocks, tiny and huge
+    scales; the edge rows (zeros, 1e-30, 1e30, -0.0, exact ties) go through both paths. The edge tokens are repeated
+    across the launch so that whole warps and single lanes of a warp meet them."""
+    PS, NT = 16, 4100 + 37
+    NP = (NT + PS - 1) // PS + 2
+    kb, vb = kv_tokens(640 + D, NT, KVH, D, kind)
+    if kind == "edge":
+        ek, ev = kv_tokens(641, 10, KVH, D, "edge")
+        for t0 in (0, 1000, 1000 + 5, 2048, 4096, NT - 10):
+            kb[t0:t0 + 10], vb[t0:t0 + 10] = ek, ev
+    slots = synth.permutation(7 + D, NP * PS)[:NT].astype(np.int64)
+    slots[synth.uniform(8 + D, NT) < 0.05] = -1
+    gk = np.array([1.0, 0.5, 2.0, 1.0, 0.3, 1.7, 0.01, 5.0][:KVH], np.float32)
+    gv = np.array([1.0, 1.0, 0.25, 4.0, 2.0, 0.5, 0.02, 3.0][:KVH], np.float32)
+    for search in (True, False):
+        cache = Cache(NP, PS, KVH, D, "hnd", fill=0xA5)
+        want = np.full(cache.bytes().shape, 0xA5, np.uint8)
+        O.write(kb, vb, want, cache.olay, slots, gk, gv, search)
+        gpu_write(cache, bf16_tensor(kb), bf16_tensor(vb), dev_t(slots), dev_t(gk), dev_t(gv), search)
+        got = cache.bytes()
+        assert np.array_equal(got, want), (D, kind, search, int((got != want).sum()))
+
+
 def test_write_from_strided_qkv_and_fewer_slots_than_tokens():
     """key / value are column slices of a fused qkv projection output; tokens beyond len(slot_mapping) are ignored"""
     NT, HQ, KVH, D, PS = 37, 32, 8, 128, 16
