@@ -601,8 +601,10 @@ def main():
                 hv[name].copy_(t.cpu())
             return SimpleNamespace(host=host, dev=dev, h=hv, d=SimpleNamespace(**dv), nbytes=sum(
                 t.numel() * t.element_size() for t in parts.values()))
-        packs = [packed(bt) for bt in batches]
-        for pk, bt in zip(packs, batches):
+        NPK = max(NBT, 2)                               # two sets of buffers even for a single batch (for the
+        pack_bt = [batches[i % NBT] for i in range(NPK)]  # leg that keeps two steps in flight)
+        packs = [packed(bt) for bt in pack_bt]
+        for pk, bt in zip(packs, pack_bt):
             pk.out_dev = torch.empty_like(bt.out)
             pk.out_host = torch.empty_like(bt.out, device="cpu").pin_memory()
             pk.dev.copy_(pk.host)
@@ -655,6 +657,42 @@ def main():
             parts_ms["host_wall"].append((time.perf_counter() - t1) * 1e3)
             for k_, a_, b_ in (("h2d", 0, 1), ("device", 1, 2), ("d2h", 2, 3)):
                 parts_ms[k_].append(e[a_].elapsed_time(e[b_]))
+        # the same steps with two of them in flight (consecutive steps use different buffers and, where the workload
+        # has two batches, different batches, as two micro-batches of a serving engine do): copies in, kernels and copies out on three streams chained by events, the host reading
+        # step i - 1's result while step i runs. Reported beside the serial figure, never instead of it.
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = [torch.cuda.Event() for _ in range(NPK)]
+        ev_run = [torch.cuda.Event() for _ in range(NPK)]
+        ev_out = [torch.cuda.Event() for _ in range(NPK)]
+
+        def piped(n_steps):
+            for i in range(n_steps):
+                j = i % NPK
+                pk = packs[j]
+                with torch.cuda.stream(s_in):
+                    if i >= NPK:
+                        s_in.wait_event(ev_run[j])           # the kernels of step i - NPK have read this buffer
+                    pk.dev.copy_(pk.host, non_blocking=True)
+                    ev_in[j].record(s_in)
+                with torch.cuda.stream(side):
+                    side.wait_event(ev_in[j])
+                    if i >= NPK:
+                        side.wait_event(ev_out[j])           # step i - NPK's output has left the device buffer
+                    pk.graph.replay()
+                    ev_run[j].record(side)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_run[j])
+                    pk.out_host.copy_(pk.out_dev, non_blocking=True)
+                    ev_out[j].record(s_out)
+                if i >= 1:
+                    ev_out[(i - 1) % NPK].synchronize()      # the caller reads the previous step's result
+            ev_out[(n_steps - 1) % NPK].synchronize()
+        piped(args.warmup)
+        barrier()
+        t0 = time.perf_counter()
+        piped(args.steps)
+        barrier()
+        piped_s = time.perf_counter() - t0
         t_end = time.perf_counter() + 0.3
         i = 0
         while time.perf_counter() < t_end:
@@ -664,11 +702,12 @@ def main():
     clocks = sampler.summary()
 
     # ---- max over ranks
-    times = torch.tensor([ms_total, e2e_s * 1e3, kt["back_to_back_ms"]["median"]], dtype=torch.float64, device=device)
+    times = torch.tensor([ms_total, e2e_s * 1e3, kt["back_to_back_ms"]["median"], (piped_s or 0.0) * 1e3],
+                         dtype=torch.float64, device=device)
     times_max = times.clone()
     if world > 1:
         dist.all_reduce(times_max, op=dist.ReduceOp.MAX)
-    ms_total_max, e2e_ms, dec_ms_max = (float(x) for x in times_max.cpu())
+    ms_total_max, e2e_ms, dec_ms_max, piped_ms = (float(x) for x in times_max.cpu())
     ms_step = ms_total_max / args.steps
     n_req = (B if args.shard else cfg["B"]) if cfg.get("sharded") else B * world   # requests of the whole job per step
     value = n_req / (ms_step * 1e-3)
@@ -750,7 +789,13 @@ def main():
             "step_hbm_gbs": alg / (ms_step * 1e-3) / 1e9,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps,
-                    "parts_ms_rank0": {k_: stats(v_)["median"] for k_, v_ in parts_ms.items()}},
+                    "parts_ms_rank0": {k_: stats(v_)["median"] for k_, v_ in parts_ms.items()},
+                    "two_steps_in_flight": {
+                        "value": n_req / (piped_ms / args.steps * 1e-3), "unit": "tokens/s",
+                        "ms_per_step": piped_ms / args.steps,
+                        "how": "consecutive steps use different buffers; copies in, kernels and copies out on three "
+                               "streams, the host reads step i - 1's output while step i runs; every step still "
+                               "copies its inputs from pinned memory and its output back"}},
             "gpu_launches": 2 * args.steps, "clocks": clocks, "device_status": status, "outputs_finite": finite,
             "e2e_output_equal": e2e_equal,
             "parity": error_record(got_s, ref_s, int(sum(per_rank)), {"requests_per_rank": per_rank,
